@@ -1,0 +1,136 @@
+/*
+ * qpack_b200_sampler.h - C ABI of the B200 (sm_100a) token sampler.
+ *
+ * A drop-in for the sampler path of the qpack engine (reference: include/qpack/engine.h:17-43,
+ * src/sampler.cpp): repetition penalty over the token history, temperature, top-k, softmax, min-p, top-p and a
+ * seeded draw, for whole batches of f32 logit rows resident in GPU memory.  Sampled ids equal the reference's
+ * for the same logits, history, parameters and seed.
+ *
+ * The reference has no FFI for this path (its boundary is the C++ class qp::Sampler); these entry points are
+ * what a binding of that class to a GPU back end needs.  Each one names the reference interface it replaces.
+ *
+ * Conventions: plain C types only; every function returns a qpb_status (0 = OK) and never throws; pointers
+ * whose name starts with d_ are device pointers on the handle's GPU, h_ are host pointers; `stream` is a
+ * cudaStream_t passed as void* (NULL = the default stream).  Calls are stream-ordered and asynchronous unless
+ * stated otherwise.  A handle is single-owner: one host thread at a time, one handle per GPU (the reference
+ * class is not thread-safe either: mutable RNG and scratch, engine.h:41-42).  Inputs are never modified
+ * (the reference takes `const float *logits`, engine.h:30).
+ */
+#ifndef QPACK_B200_SAMPLER_H
+#define QPACK_B200_SAMPLER_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define QPB_API __attribute__((visibility("default")))
+#else
+#define QPB_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  QPB_OK = 0,
+  QPB_ERR_INVALID = 1,        /* bad argument (null pointer, non-positive size, row count above the handle's) */
+  QPB_ERR_CUDA = 2,           /* a CUDA runtime call failed; see qpb_sampler_last_error */
+  QPB_ERR_NCCL = 3,           /* an NCCL call failed or NCCL could not be loaded */
+  QPB_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait gave up (reported by qpb_sampler_check) */
+  QPB_ERR_UNSUPPORTED = 5,    /* a size outside the documented limits */
+  QPB_ERR_INTERNAL = 6        /* a device-side capacity check failed (reported by qpb_sampler_check) */
+} qpb_status;
+
+/* Same fields, order, defaults' meaning and 32-byte layout as qp::SamplerParams (engine.h:17-25):
+ * temperature <= 0: greedy; top_k <= 0: off; top_p >= 1: off; min_p <= 0: off; repeat_penalty == 1: off;
+ * repeat_last_n: history window (negative: whole history).  seed 0 ("random" in the reference,
+ * src/sampler.cpp:8) is replaced by a value from the host's entropy source. */
+typedef struct {
+  float temperature;
+  int32_t top_k;
+  float top_p;
+  float min_p;
+  float repeat_penalty;
+  int32_t repeat_last_n;
+  uint64_t seed;
+} qpb_sampler_params;
+
+typedef struct qpb_sampler qpb_sampler; /* opaque; owns per-row RNG state and device scratch */
+
+/* Replaces qp::Sampler::Sampler (src/sampler.cpp:8), for max_rows independent rows on GPU `device`.
+ * Allocates device memory; synchronous. */
+QPB_API int qpb_sampler_create(qpb_sampler **out, int device, int max_rows);
+QPB_API int qpb_sampler_destroy(qpb_sampler *s);
+
+/* Parameters and seeds (constructor argument of qp::Sampler, engine.h:29).  n == max_rows: one block per row.
+ * n == 1: one block shared by every row, row r seeded with params->seed + r (row 0 reproduces the reference's
+ * single sampler).  Re-seeds every row's MT19937-64 stream.  Synchronous. */
+QPB_API int qpb_sampler_set_params(qpb_sampler *s, const qpb_sampler_params *params, int n);
+
+/* Replaces qp::Sampler::sample (engine.h:30) for n_rows rows: d_out_ids[r] = sampled token of row r.
+ * d_logits: [n_rows][row_stride] f32, vocab <= row_stride.  d_history: [n_rows][hist_stride] token ids (may be
+ * NULL); d_hist_len[r] (<= hist_stride) entries of row r are visible, or hist_len_all for every row when
+ * d_hist_len is NULL (the hist_len argument of dist, engine.h:34).  Out-of-range history ids are skipped
+ * (src/sampler.cpp:36). */
+QPB_API int qpb_sampler_sample_batch(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
+                             const int32_t *d_history, int64_t hist_stride, const int32_t *d_hist_len,
+                             int hist_len_all, int32_t *d_out_ids, void *stream);
+
+/* Replaces qp::Sampler::dist (engine.h:31-34, src/sampler.cpp:29-56): row r's distribution as (id, probability)
+ * pairs, most likely first, into d_dist_ids / d_dist_p [n_rows][max_out] (first max_out pairs) with the full
+ * pair count in d_dist_count[r].  If d_out_ids is not NULL the draw of qp::Sampler::draw (src/sampler.cpp:58-63)
+ * is made as well, otherwise the RNG is left untouched.  Rows whose candidate budget top_k + window exceeds
+ * 768 (top_k off, or very large) report their pairs in no particular order. */
+QPB_API int qpb_sampler_dist_batch(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
+                           const int32_t *d_history, int64_t hist_stride, const int32_t *d_hist_len, int hist_len_all,
+                           int32_t *d_dist_ids, float *d_dist_p, int32_t *d_dist_count, int max_out,
+                           int32_t *d_out_ids, void *stream);
+
+/* The same call for callers that hold logits in host memory, as every qp::Model::step does
+ * (include/qpack/qpack.h:137): copies h_logits / h_history to the GPU, samples, copies the ids back and
+ * returns after they have arrived.  Synchronous; checks the device status. */
+QPB_API int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
+                            const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len,
+                            int hist_len_all, int32_t *h_out_ids);
+
+/* Synchronises `stream`, reads and clears the device status word of the calls issued so far. */
+QPB_API int qpb_sampler_check(qpb_sampler *s, void *stream);
+
+/* Per-row RNG state for checkpoint / resume (the reference's std::mt19937_64 member, engine.h:41):
+ * 312 state words followed by the number of words drawn so far.  Synchronous. */
+QPB_API int qpb_sampler_rng_get(qpb_sampler *s, int row, uint64_t *h_state313);
+QPB_API int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state313);
+
+/* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1, 2, 4 or 8. */
+QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
+
+/* Number of kernels this handle has launched so far. */
+QPB_API int64_t qpb_sampler_launch_count(const qpb_sampler *s);
+
+/* Message of the last failing call on this handle (empty string if none).  The pointer stays valid until the
+ * next call on the handle. */
+QPB_API const char *qpb_sampler_last_error(const qpb_sampler *s);
+
+/* ---- vocabulary-sharded rows (a tensor-parallel LM head; no counterpart in the single-device reference; the
+ * result equals qp::Sampler::sample on the concatenated row) ---------------------------------------------------
+ * Step 1, on every GPU: the exact local winners of its vocab_local columns [id_offset, id_offset + vocab_local)
+ * as 64-bit (key, global id) entries, d_cand [n_rows][slots], slots from qpb_sampler_cand_slots.
+ * Step 2: all-gather of d_cand over the GPUs into [n_shards][n_rows][slots] (the caller's collective, or
+ * qpb_sampler_sample_sharded).  Step 3: merge, filter and draw on the gathered entries. */
+QPB_API int qpb_sampler_cand_slots(qpb_sampler *s, int vocab_total, int vocab_local_max, int *slots);
+QPB_API int qpb_sampler_local_candidates(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows,
+                                 int vocab_local, int vocab_total, int id_offset, const int32_t *d_history,
+                                 int64_t hist_stride, const int32_t *d_hist_len, int hist_len_all, uint64_t *d_cand,
+                                 int slots, void *stream);
+QPB_API int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_shards, int n_rows, int slots,
+                             int vocab_total, const int32_t *d_history, int64_t hist_stride,
+                             const int32_t *d_hist_len, int hist_len_all, int32_t *d_dist_ids, float *d_dist_p,
+                             int32_t *d_dist_count, int max_out, int32_t *d_out_ids, void *stream);
+
+/* Debug aid for the tests: out[i] = the device's expf(x[i]) (the C library's expf bit for bit), n floats. */
+QPB_API int qpb_debug_expf(const float *d_x, float *d_out, int n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QPACK_B200_SAMPLER_H */

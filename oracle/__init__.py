@@ -1,0 +1,268 @@
+"""ctypes bindings for the two CPU checkers.  TEST INFRASTRUCTURE: imported only by tests/, the smoke
+check and the CPU leg of bench.py; the product package never imports this module.
+
+* ``Oracle``  : the plain-C restatement (oracle/sampler_oracle.c), always available (built by oracle/Makefile).
+* ``Ref``     : the reference's own ``qp::Sampler`` (src/sampler.cpp) compiled into oracle/_ref/; present when
+  the reference sources were available at build time (the prebuilt library travels with the tree).
+
+Both expose the same calls: sample / dist / draw / accept for one sampler object and ``sample_rows`` for a
+batch with one fresh sampler per row.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(_HERE, "_build", "libsampler_oracle.so")
+REF_SO = os.path.join(_HERE, "_ref", "libqpack_ref.so")
+
+
+class Params(C.Structure):
+    """Byte-compatible with qp::SamplerParams (include/qpack/engine.h:17-25)."""
+
+    _fields_ = [
+        ("temperature", C.c_float),
+        ("top_k", C.c_int32),
+        ("top_p", C.c_float),
+        ("min_p", C.c_float),
+        ("repeat_penalty", C.c_float),
+        ("repeat_last_n", C.c_int32),
+        ("seed", C.c_uint64),
+    ]
+
+
+PARAMS_DTYPE = np.dtype(
+    [
+        ("temperature", "<f4"),
+        ("top_k", "<i4"),
+        ("top_p", "<f4"),
+        ("min_p", "<f4"),
+        ("repeat_penalty", "<f4"),
+        ("repeat_last_n", "<i4"),
+        ("seed", "<u8"),
+    ]
+)
+assert PARAMS_DTYPE.itemsize == 32 and C.sizeof(Params) == 32
+
+
+def make_params(n=1, temperature=0.7, top_k=40, top_p=0.9, min_p=0.05, repeat_penalty=1.1, repeat_last_n=64, seed=1):
+    """Structured array of n parameter blocks; every argument may be a scalar or a length-n array.
+    Defaults are the reference's (engine.h:18-24) except seed (0 = non-deterministic there, never used here)."""
+    p = np.zeros(n, dtype=PARAMS_DTYPE)
+    p["temperature"] = temperature
+    p["top_k"] = top_k
+    p["top_p"] = top_p
+    p["min_p"] = min_p
+    p["repeat_penalty"] = repeat_penalty
+    p["repeat_last_n"] = repeat_last_n
+    p["seed"] = seed
+    return p
+
+
+def build(force: bool = False) -> None:
+    """Run oracle/Makefile (C restatement always; the reference build when its sources are present)."""
+    ref_dir = os.environ.get("QPACK_REFERENCE_DIR", "/root/reference")
+    have_src = os.path.exists(os.path.join(ref_dir, "src", "sampler.cpp"))
+    src = os.path.join(_HERE, "sampler_oracle.c")
+    old = os.path.exists(ORACLE_SO) and os.path.getmtime(ORACLE_SO) < os.path.getmtime(src)
+    if force or old or not os.path.exists(ORACLE_SO) or (have_src and not os.path.exists(REF_SO)):
+        subprocess.run(["make", "-C", _HERE, "REF=" + ref_dir], check=True, capture_output=True)
+
+
+def _ptr(a, ty):
+    return a.ctypes.data_as(C.POINTER(ty)) if a is not None else None
+
+
+class _Base:
+    _prefix = ""
+    _lib = None
+
+    def __init__(self, params):
+        """params: a length-1 structured array (make_params) or a Params."""
+        if isinstance(params, np.ndarray):
+            params = Params.from_buffer_copy(params[:1].tobytes())
+        self._h = getattr(self._lib, self._prefix + "create")(C.byref(params))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            getattr(self._lib, self._prefix + "destroy")(self._h)
+            self._h = None
+
+    def dist(self, logits, history=None, hist_len=-1):
+        logits = np.ascontiguousarray(logits, dtype=np.float32)
+        V = logits.shape[0]
+        h = np.ascontiguousarray(history if history is not None else [], dtype=np.int32)
+        ids = np.empty(V, np.int32)
+        pr = np.empty(V, np.float32)
+        n = getattr(self._lib, self._prefix + "dist")(
+            self._h, _ptr(logits, C.c_float), V, _ptr(h, C.c_int32), h.shape[0], hist_len, _ptr(ids, C.c_int32),
+            _ptr(pr, C.c_float), V)
+        return ids[:n].copy(), pr[:n].copy()
+
+    def draw(self, ids, pr):
+        ids = np.ascontiguousarray(ids, np.int32)
+        pr = np.ascontiguousarray(pr, np.float32)
+        return getattr(self._lib, self._prefix + "draw")(self._h, _ptr(ids, C.c_int32), _ptr(pr, C.c_float), len(ids))
+
+    def accept(self, ids, pr, token):
+        ids = np.ascontiguousarray(ids, np.int32)
+        pr = np.ascontiguousarray(pr, np.float32)
+        repl = C.c_int32(-1)
+        ok = getattr(self._lib, self._prefix + "accept")(
+            self._h, _ptr(ids, C.c_int32), _ptr(pr, C.c_float), len(ids), int(token), C.byref(repl))
+        return bool(ok), repl.value
+
+    def sample(self, logits, history=None):
+        ids, pr = self.dist(logits, history)
+        return self.draw(ids, pr)
+
+
+def _common_sigs(lib, pre):
+    f = getattr(lib, pre + "create")
+    f.restype = C.c_void_p
+    f.argtypes = [C.POINTER(Params)]
+    f = getattr(lib, pre + "destroy")
+    f.restype = None
+    f.argtypes = [C.c_void_p]
+    f = getattr(lib, pre + "dist")
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_int32), C.c_int64, C.c_int64,
+                  C.POINTER(C.c_int32), C.POINTER(C.c_float), C.c_int]
+    f = getattr(lib, pre + "draw")
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_float), C.c_int]
+    f = getattr(lib, pre + "accept")
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_float), C.c_int, C.c_int32, C.POINTER(C.c_int32)]
+
+
+def _rows_args(params, logits, history, hist_len, max_out):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    B, V = logits.shape
+    params = np.ascontiguousarray(params, dtype=PARAMS_DTYPE)
+    assert params.shape[0] in (1, B)
+    if history is not None:
+        history = np.ascontiguousarray(history, dtype=np.int32)
+        assert history.shape[0] == B
+        if hist_len is None:
+            hist_len = np.full(B, history.shape[1], np.int32)
+        hist_len = np.ascontiguousarray(hist_len, dtype=np.int32)
+        hstride = history.shape[1]
+    else:
+        hist_len, hstride = None, 0
+    out_ids = np.empty(B, np.int32)
+    out_cnt = np.empty(B, np.int32)
+    d_ids = np.full((B, max_out), -1, np.int32) if max_out > 0 else None
+    d_p = np.zeros((B, max_out), np.float32) if max_out > 0 else None
+    return logits, B, V, params, history, hist_len, hstride, out_ids, out_cnt, d_ids, d_p
+
+
+class Oracle(_Base):
+    _prefix = "orc_"
+
+    @classmethod
+    def load(cls):
+        if cls._lib is None:
+            build()
+            lib = C.CDLL(ORACLE_SO)
+            _common_sigs(lib, "orc_")
+            lib.orc_next_word.restype = C.c_uint64
+            lib.orc_next_word.argtypes = [C.c_void_p]
+            lib.orc_next_uniform.restype = C.c_double
+            lib.orc_next_uniform.argtypes = [C.c_void_p]
+            lib.orc_words_drawn.restype = C.c_uint64
+            lib.orc_words_drawn.argtypes = [C.c_void_p]
+            lib.orc_expf_vec.restype = None
+            lib.orc_expf_vec.argtypes = [C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_int64]
+            lib.orc_sample_rows.restype = None
+            lib.orc_sample_rows.argtypes = [
+                C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int32),
+                C.c_int64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_int32)]
+            cls._lib = lib
+        return cls
+
+    def __init__(self, params):
+        self.load()
+        super().__init__(params)
+
+    @classmethod
+    def expf(cls, x):
+        """The C library's expf, elementwise (float32 in, float32 out)."""
+        cls.load()
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty_like(x)
+        cls._lib.orc_expf_vec(_ptr(x, C.c_float), _ptr(out, C.c_float), x.size)
+        return out
+
+    def next_word(self):
+        return self._lib.orc_next_word(self._h)
+
+    def next_uniform(self):
+        return self._lib.orc_next_uniform(self._h)
+
+    def words_drawn(self):
+        return self._lib.orc_words_drawn(self._h)
+
+    @classmethod
+    def sample_rows(cls, params, logits, history=None, hist_len=None, max_out=0):
+        """One fresh sampler per row.  Returns dict(ids, count, dist_ids, dist_p, consumed)."""
+        cls.load()
+        logits, B, V, params, history, hist_len, hstride, out_ids, out_cnt, d_ids, d_p = _rows_args(
+            params, logits, history, hist_len, max_out)
+        consumed = np.empty(B, np.int32)
+        cls._lib.orc_sample_rows(
+            params.ctypes.data, params.shape[0], _ptr(logits, C.c_float), V, B, V, _ptr(history, C.c_int32), hstride,
+            _ptr(hist_len, C.c_int32), _ptr(out_ids, C.c_int32), _ptr(out_cnt, C.c_int32), _ptr(d_ids, C.c_int32),
+            _ptr(d_p, C.c_float), max_out, _ptr(consumed, C.c_int32))
+        return dict(ids=out_ids, count=out_cnt, dist_ids=d_ids, dist_p=d_p, consumed=consumed)
+
+
+class Ref(_Base):
+    _prefix = "ref_"
+
+    @classmethod
+    def available(cls):
+        build()
+        return os.path.exists(REF_SO)
+
+    @classmethod
+    def load(cls):
+        if cls._lib is None:
+            build()
+            lib = C.CDLL(REF_SO)
+            _common_sigs(lib, "ref_")
+            lib.ref_sample_rows.restype = C.c_double
+            lib.ref_sample_rows.argtypes = [
+                C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int64, C.c_int, C.c_int, C.POINTER(C.c_int32),
+                C.c_int64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                C.POINTER(C.c_float), C.c_int, C.c_int]
+            lib.ref_hardware_threads.restype = C.c_int
+            cls._lib = lib
+        return cls
+
+    def __init__(self, params):
+        self.load()
+        super().__init__(params)
+
+    @classmethod
+    def hardware_threads(cls):
+        cls.load()
+        return cls._lib.ref_hardware_threads()
+
+    @classmethod
+    def sample_rows(cls, params, logits, history=None, hist_len=None, max_out=0, threads=1):
+        """One fresh qp::Sampler per row, rows fanned over `threads` host threads.
+        Returns dict(ids, count, dist_ids, dist_p, seconds)."""
+        cls.load()
+        logits, B, V, params, history, hist_len, hstride, out_ids, out_cnt, d_ids, d_p = _rows_args(
+            params, logits, history, hist_len, max_out)
+        sec = cls._lib.ref_sample_rows(
+            params.ctypes.data, params.shape[0], _ptr(logits, C.c_float), V, B, V, _ptr(history, C.c_int32), hstride,
+            _ptr(hist_len, C.c_int32), _ptr(out_ids, C.c_int32), _ptr(out_cnt, C.c_int32), _ptr(d_ids, C.c_int32),
+            _ptr(d_p, C.c_float), max_out, threads)
+        return dict(ids=out_ids, count=out_cnt, dist_ids=d_ids, dist_p=d_p, seconds=sec)

@@ -1,0 +1,57 @@
+"""Loads the CUDA library through its C ABI (include/qpack_b200_sampler.h).  There is no fallback: if the
+library is missing or cannot be loaded the import of the sampler fails with the reason."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqpack_b200_sampler.so")
+
+OK, ERR_INVALID, ERR_CUDA, ERR_NCCL, ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED, ERR_INTERNAL = range(7)
+STATUS_NAMES = ["QPB_OK", "QPB_ERR_INVALID", "QPB_ERR_CUDA", "QPB_ERR_NCCL", "QPB_ERR_DEVICE_TIMEOUT",
+                "QPB_ERR_UNSUPPORTED", "QPB_ERR_INTERNAL"]
+
+_i32p, _f32p, _u64p, _vp = C.POINTER(C.c_int32), C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.c_void_p
+
+# name -> (restype, argtypes); device pointers are passed as integers (c_void_p)
+SIGNATURES = {
+    "qpb_sampler_create": (C.c_int, [C.POINTER(_vp), C.c_int, C.c_int]),
+    "qpb_sampler_destroy": (C.c_int, [_vp]),
+    "qpb_sampler_set_params": (C.c_int, [_vp, _vp, C.c_int]),
+    "qpb_sampler_sample_batch": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp, _vp]),
+    "qpb_sampler_dist_batch": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp, _vp,
+                                         _vp, C.c_int, _vp, _vp]),
+    "qpb_sampler_sample_host": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp]),
+    "qpb_sampler_check": (C.c_int, [_vp, _vp]),
+    "qpb_sampler_rng_get": (C.c_int, [_vp, C.c_int, _vp]),
+    "qpb_sampler_rng_set": (C.c_int, [_vp, C.c_int, _vp]),
+    "qpb_sampler_set_cluster": (C.c_int, [_vp, C.c_int]),
+    "qpb_sampler_launch_count": (C.c_int64, [_vp]),
+    "qpb_sampler_last_error": (C.c_char_p, [_vp]),
+    "qpb_sampler_cand_slots": (C.c_int, [_vp, C.c_int, C.c_int, C.POINTER(C.c_int)]),
+    "qpb_sampler_local_candidates": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64,
+                                               _vp, C.c_int, _vp, C.c_int, _vp]),
+    "qpb_sampler_merge_sample": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int,
+                                           _vp, _vp, _vp, C.c_int, _vp, _vp]),
+    "qpb_debug_expf": (C.c_int, [_vp, _vp, C.c_int, _vp]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """The loaded library with every declared entry point bound; raises if anything is missing."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m qpack_b200.build` (needs nvcc); "
+                "there is no CPU fallback")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            f = getattr(lib, name)  # AttributeError if the symbol is not exported
+            f.restype = res
+            f.argtypes = args
+        _lib = lib
+    return _lib

@@ -1,0 +1,160 @@
+// Shared device-side pieces of the B200 sampler: parameter block, order-preserving keys, the bulk-copy /
+// mbarrier wrappers, the bit-exact expf and the per-row MT19937-64 step.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace qpb {
+
+// Device copy of the reference parameter block (qp::SamplerParams, include/qpack/engine.h:17-25); same layout.
+struct RowParams {
+  float temperature;
+  int top_k;
+  float top_p;
+  float min_p;
+  float repeat_penalty;
+  int repeat_last_n;
+  unsigned long long seed;
+};
+static_assert(sizeof(RowParams) == 32, "parameter block layout");
+
+// Status word written by kernels (0 = fine).  Bits are OR-ed, the host turns them into an error code.
+enum : int {
+  ST_COPY_TIMEOUT = 1,    // a bounded wait on a bulk copy gave up
+  ST_CAPACITY = 2,        // a candidate buffer would have overflowed (host sizing bug)
+  ST_PEN_TABLE_FULL = 4,  // penalty hash table full (host sizing bug)
+};
+
+constexpr int MT_N = 312;
+constexpr int MT_M = 156;
+
+// ---- order-preserving keys --------------------------------------------------------------------------------
+// key(a) > key(b)  <=>  a > b as floats; -0.0 and +0.0 share one key (they compare equal in the reference and
+// the index breaks the tie, src/sampler.cpp:16,43).  NaN (undefined behaviour in the reference's comparator)
+// is ordered below -inf: key 1.  Key 0 is never produced and marks "no entry".
+__device__ __forceinline__ uint32_t f2key(float f) {
+  uint32_t b = __float_as_uint(f);
+  if ((b & 0x7fffffffu) > 0x7f800000u) return 1u;
+  if (b == 0x80000000u) b = 0u;
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
+}
+// (value descending, index ascending) as one unsigned compare: larger composite = earlier in the order.
+__device__ __forceinline__ unsigned long long make_comp(uint32_t key, uint32_t id) {
+  return ((unsigned long long)key << 32) | (unsigned long long)(0xffffffffu - id);
+}
+__device__ __forceinline__ uint32_t comp_key(unsigned long long c) { return (uint32_t)(c >> 32); }
+__device__ __forceinline__ int comp_id(unsigned long long c) { return (int)(0xffffffffu - (uint32_t)c); }
+
+// ---- shared-memory barriers and bulk copies (non-multicast, own CTA only) ------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after a fixed number of polls so that a lost copy can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+  for (int i = 0; i < (1 << 22); ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// global -> this CTA's shared memory, completion counted in bytes on `bar`.  dst, src 16-byte aligned, bytes a
+// multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// ---- expf, bit-for-bit the C library's ---------------------------------------------------------------------
+// The reference computes its softmax numerators with the C library's expf (src/sampler.cpp:47).  glibc 2.39 on
+// x86-64 with FMA implements it as the ARM optimized-routines single-precision exp evaluated in double:
+// x*32/ln2 = k + r, 2^(k/32) from a 32-entry table, a cubic in r, every multiply-add fused.  Restated here with
+// explicit fma so that the device returns the same float for every input; verified on the host against the
+// library for all 2^31 non-positive inputs.
+__device__ __constant__ const unsigned long long kExp2Tab[32] = {
+    0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,
+    0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,
+    0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,
+    0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,
+    0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,
+    0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,
+    0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
+    0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
+
+__device__ __forceinline__ float expf_libm(float x) {
+  const uint32_t ux = __float_as_uint(x);
+  const uint32_t abstop = (ux >> 20) & 0x7ffu;
+  if (abstop >= 0x42bu) {  // |x| >= 88 or NaN
+    if (ux == 0xff800000u) return 0.0f;
+    if (abstop >= 0x7f8u) return x + x;
+    if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);
+    if (x < -0x1.9fe368p6f) return 0.0f;
+    if (x < -0x1.9d1d9ep6f) return __fmul_rn(0x1.4p-75f, 0x1.4p-75f);
+  }
+  const double InvLn2N = 0x1.71547652b82fep+0 * 32.0;
+  const double Shift = 0x1.8p+52;
+  const double C0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
+  const double C1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+  const double C2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+  const double xd = (double)x;
+  double kd = __fma_rn(InvLn2N, xd, Shift);
+  const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+  kd = __dsub_rn(kd, Shift);
+  const double r = __fma_rn(InvLn2N, xd, -kd);
+  const unsigned long long t = kExp2Tab[ki & 31u] + (ki << 47);
+  const double s = __longlong_as_double((long long)t);
+  const double z = __fma_rn(C0, r, C1);
+  const double r2 = __dmul_rn(r, r);
+  double y = __fma_rn(C2, r, 1.0);
+  y = __fma_rn(z, r2, y);
+  y = __dmul_rn(y, s);
+  return __double2float_rn(y);
+}
+
+// ---- MT19937-64, one word per call, state in global memory ----------------------------------------------------
+// The reference owns one std::mt19937_64 per sampler (engine.h:41) and draws one 64-bit word per
+// uniform_real_distribution<double>(0,1) variate (sampler.cpp:60,68).  The state array is advanced lazily, one
+// element per draw, which performs the same in-place updates in the same order as the engine's block
+// regeneration; `drawn` counts the words taken so far.
+__device__ __forceinline__ unsigned long long mt_next(unsigned long long *mt, unsigned int *drawn) {
+  const unsigned int d = *drawn;
+  const int k = (int)(d % MT_N);
+  const int k1 = (k + 1 == MT_N) ? 0 : k + 1;
+  const int km = (k + MT_M >= MT_N) ? k + MT_M - MT_N : k + MT_M;
+  const unsigned long long y = (mt[k] & 0xFFFFFFFF80000000ULL) | (mt[k1] & 0x7FFFFFFFULL);
+  unsigned long long x = mt[km] ^ (y >> 1) ^ ((y & 1ULL) ? 0xB5026F5AA96619E9ULL : 0ULL);
+  mt[k] = x;
+  *drawn = d + 1;
+  x ^= (x >> 29) & 0x5555555555555555ULL;
+  x ^= (x << 17) & 0x71D67FFFEDA60000ULL;
+  x ^= (x << 37) & 0xFFF7EEE000000000ULL;
+  x ^= x >> 43;
+  return x;
+}
+// libstdc++ generate_canonical<double, 53> on a 64-bit engine: (double)word * 2^-64, clamped below 1.
+__device__ __forceinline__ double word_to_uniform(unsigned long long w) {
+  double u = __ull2double_rn(w) * 0x1p-64;
+  if (u >= 1.0) u = 0x1.fffffffffffffp-1;
+  return u;
+}
+
+}  // namespace qpb

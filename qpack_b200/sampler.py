@@ -1,0 +1,211 @@
+"""Host-side mirror of the reference sampler interface (qp::SamplerParams / qp::Sampler,
+include/qpack/engine.h:17-43) on top of the C ABI.  torch is used for device memory and streams only."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from .synth import PARAMS_DTYPE, make_params
+
+
+class SamplerError(RuntimeError):
+    """A non-zero status from the C ABI (the engine's convention is to throw std::runtime_error)."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{_lib.STATUS_NAMES[code] if 0 <= code < len(_lib.STATUS_NAMES) else code}: {msg}")
+        self.code = code
+
+
+@dataclass
+class SamplerParams:
+    """Same names and defaults as qp::SamplerParams (engine.h:17-25)."""
+
+    temperature: float = 0.7
+    top_k: int = 40
+    top_p: float = 0.9
+    min_p: float = 0.05
+    repeat_penalty: float = 1.1
+    repeat_last_n: int = 64
+    seed: int = 0
+
+    def to_array(self) -> np.ndarray:
+        return make_params(1, self.temperature, self.top_k, self.top_p, self.min_p, self.repeat_penalty,
+                           self.repeat_last_n, self.seed)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+class BatchSampler:
+    """One handle on one GPU for up to max_rows independent rows (one reference Sampler per row)."""
+
+    def __init__(self, max_rows: int, device: int = 0):
+        self._lib = _lib.load()
+        self._h = C.c_void_p()
+        self.device = int(device)
+        self.max_rows = int(max_rows)
+        rc = self._lib.qpb_sampler_create(C.byref(self._h), self.device, self.max_rows)
+        if rc != 0:
+            self._h = C.c_void_p()
+            raise SamplerError(rc, "qpb_sampler_create failed (is an sm_100 GPU visible?)")
+        self._tdev = torch.device("cuda", self.device)
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            self._lib.qpb_sampler_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _ck(self, rc: int):
+        if rc != 0:
+            raise SamplerError(rc, (self._lib.qpb_sampler_last_error(self._h) or b"").decode())
+
+    def set_params(self, params):
+        """params: SamplerParams (shared by every row, row r seeded with seed + r) or a structured array with one
+        block per row (synth.PARAMS_DTYPE)."""
+        if isinstance(params, SamplerParams):
+            params = params.to_array()
+        params = np.ascontiguousarray(params, dtype=PARAMS_DTYPE)
+        self._ck(self._lib.qpb_sampler_set_params(self._h, params.ctypes.data, int(params.shape[0])))
+
+    def set_cluster(self, cluster: int):
+        self._ck(self._lib.qpb_sampler_set_cluster(self._h, int(cluster)))
+
+    def _stream(self, stream):
+        if stream is None:
+            stream = torch.cuda.current_stream(self._tdev)
+        return stream.cuda_stream
+
+    @staticmethod
+    def _hist_args(history, hist_len):
+        if history is None:
+            return None, 0, None, 0
+        assert history.dtype == torch.int32 and history.dim() == 2 and history.is_contiguous()
+        if isinstance(hist_len, torch.Tensor):
+            assert hist_len.dtype == torch.int32
+            return history.data_ptr(), history.shape[1], hist_len.data_ptr(), 0
+        return history.data_ptr(), history.shape[1], None, int(history.shape[1] if hist_len is None else hist_len)
+
+    def sample(self, logits: torch.Tensor, history: Optional[torch.Tensor] = None, hist_len=None,
+               out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """qp::Sampler::sample (engine.h:30) for every row of logits [B, V] (f32, on this GPU).  Asynchronous."""
+        assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+        B, V = logits.shape
+        if out is None:
+            out = torch.empty(B, dtype=torch.int32, device=logits.device)
+        hp, hs, hl, hla = self._hist_args(history, hist_len)
+        self._ck(self._lib.qpb_sampler_sample_batch(self._h, logits.data_ptr(), logits.stride(0), B, V, hp, hs, hl, hla,
+                                                    out.data_ptr(), self._stream(stream)))
+        return out
+
+    def dist(self, logits: torch.Tensor, history: Optional[torch.Tensor] = None, hist_len=None, max_out: int = 64,
+             draw: bool = False, stream=None):
+        """qp::Sampler::dist (engine.h:31-34) per row: (ids [B, max_out], p [B, max_out], count [B]) and, with
+        draw=True, the sampled ids [B] as a fourth element."""
+        assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+        B, V = logits.shape
+        ids = torch.full((B, max_out), -1, dtype=torch.int32, device=logits.device)
+        p = torch.zeros((B, max_out), dtype=torch.float32, device=logits.device)
+        cnt = torch.zeros(B, dtype=torch.int32, device=logits.device)
+        out = torch.empty(B, dtype=torch.int32, device=logits.device) if draw else None
+        hp, hs, hl, hla = self._hist_args(history, hist_len)
+        self._ck(self._lib.qpb_sampler_dist_batch(self._h, logits.data_ptr(), logits.stride(0), B, V, hp, hs, hl, hla,
+                                                  ids.data_ptr(), p.data_ptr(), cnt.data_ptr(), max_out, _ptr(out),
+                                                  self._stream(stream)))
+        return (ids, p, cnt, out) if draw else (ids, p, cnt)
+
+    def sample_host(self, logits: np.ndarray, history: Optional[np.ndarray] = None, hist_len=None,
+                    out: Optional[np.ndarray] = None) -> np.ndarray:
+        """The same for logits in host memory (numpy, or a pinned torch tensor's .numpy()): copies in, samples,
+        copies the ids back; synchronous."""
+        assert logits.dtype == np.float32 and logits.ndim == 2 and logits.strides[1] == 4
+        B, V = logits.shape
+        if out is None:
+            out = np.empty(B, np.int32)
+        hp, hs, hl, hla = None, 0, None, 0
+        if history is not None:
+            assert history.dtype == np.int32 and history.ndim == 2 and history.flags.c_contiguous
+            hp, hs = history.ctypes.data, history.shape[1]
+            if isinstance(hist_len, np.ndarray):
+                assert hist_len.dtype == np.int32
+                hl = hist_len.ctypes.data
+            else:
+                hla = int(history.shape[1] if hist_len is None else hist_len)
+        self._ck(self._lib.qpb_sampler_sample_host(self._h, logits.ctypes.data, logits.strides[0] // 4, B, V, hp, hs, hl,
+                                                   hla, out.ctypes.data))
+        return out
+
+    def check(self, stream=None):
+        """Synchronise and raise if a kernel reported a device-side problem."""
+        self._ck(self._lib.qpb_sampler_check(self._h, self._stream(stream)))
+
+    def rng_get(self, row: int) -> np.ndarray:
+        st = np.empty(313, np.uint64)
+        self._ck(self._lib.qpb_sampler_rng_get(self._h, int(row), st.ctypes.data))
+        return st
+
+    def rng_set(self, row: int, state: np.ndarray):
+        st = np.ascontiguousarray(state, np.uint64)
+        assert st.shape == (313,)
+        self._ck(self._lib.qpb_sampler_rng_set(self._h, int(row), st.ctypes.data))
+
+    @property
+    def launches(self) -> int:
+        return int(self._lib.qpb_sampler_launch_count(self._h))
+
+    # ---- vocabulary-sharded rows ----
+    def cand_slots(self, vocab_total: int, vocab_local_max: int) -> int:
+        n = C.c_int(0)
+        self._ck(self._lib.qpb_sampler_cand_slots(self._h, int(vocab_total), int(vocab_local_max), C.byref(n)))
+        return n.value
+
+    def local_candidates(self, logits: torch.Tensor, vocab_total: int, id_offset: int, slots: int,
+                         history=None, hist_len=None, out=None, stream=None) -> torch.Tensor:
+        assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+        B, Vl = logits.shape
+        if out is None:
+            out = torch.empty((B, slots), dtype=torch.int64, device=logits.device)
+        hp, hs, hl, hla = self._hist_args(history, hist_len)
+        self._ck(self._lib.qpb_sampler_local_candidates(self._h, logits.data_ptr(), logits.stride(0), B, Vl,
+                                                        int(vocab_total), int(id_offset), hp, hs, hl, hla,
+                                                        out.data_ptr(), int(slots), self._stream(stream)))
+        return out
+
+    def merge_sample(self, cand_all: torch.Tensor, vocab_total: int, history=None, hist_len=None, max_out: int = 0,
+                     stream=None):
+        """cand_all: [n_shards, B, slots] int64 gathered candidate entries.  Returns ids [B] (and the distribution
+        when max_out > 0)."""
+        assert cand_all.dtype == torch.int64 and cand_all.dim() == 3 and cand_all.is_contiguous()
+        G, B, slots = cand_all.shape
+        out = torch.empty(B, dtype=torch.int32, device=cand_all.device)
+        ids = p = cnt = None
+        if max_out > 0:
+            ids = torch.full((B, max_out), -1, dtype=torch.int32, device=cand_all.device)
+            p = torch.zeros((B, max_out), dtype=torch.float32, device=cand_all.device)
+            cnt = torch.zeros(B, dtype=torch.int32, device=cand_all.device)
+        hp, hs, hl, hla = self._hist_args(history, hist_len)
+        self._ck(self._lib.qpb_sampler_merge_sample(self._h, cand_all.data_ptr(), G, B, slots, int(vocab_total), hp, hs,
+                                                    hl, hla, _ptr(ids), _ptr(p), _ptr(cnt), max_out, out.data_ptr(),
+                                                    self._stream(stream)))
+        return (out, ids, p, cnt) if max_out > 0 else out
+
+
+def device_expf(x: torch.Tensor) -> torch.Tensor:
+    """The device's restatement of the C library's expf, for the tests."""
+    lib = _lib.load()
+    out = torch.empty_like(x)
+    rc = lib.qpb_debug_expf(x.data_ptr(), out.data_ptr(), x.numel(), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise SamplerError(rc, "qpb_debug_expf")
+    return out

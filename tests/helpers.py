@@ -1,0 +1,48 @@
+"""Shared comparison code of the parity tests."""
+import numpy as np
+
+P_TOL = 1e-5  # absolute tolerance on post-filter probabilities
+BOUNDARY_TOL = 1e-6  # an id mismatch is tolerated only if the draw lies this close to a CDF boundary
+
+
+def small_case(golden, i):
+    return (golden[f"small{i}_logits"], golden[f"small{i}_hist"], golden[f"small{i}_hist_len"],
+            golden[f"small{i}_params"], golden[f"small{i}_ids"], golden[f"small{i}_count"],
+            golden[f"small{i}_dist_ids"], golden[f"small{i}_dist_p"])
+
+
+def near_boundary(uniform, probs):
+    """True if `uniform` lies within BOUNDARY_TOL of a boundary of the CDF of `probs` (in order)."""
+    cdf = np.cumsum(probs.astype(np.float64))
+    return bool(np.any(np.abs(cdf - uniform) <= BOUNDARY_TOL))
+
+
+def compare_rows(got_ids, got_cnt, got_dids, got_dp, exp, uniforms=None, ordered=True):
+    """Compares device outputs with a checker's dict(ids, count, dist_ids, dist_p).  Returns a report dict;
+    raises AssertionError on any difference outside the stated tolerances.
+    ordered=False: the pairs of a row are compared as a set (rows of the whole-row kernel)."""
+    B = len(exp["ids"])
+    rep = dict(rows=B, id_mismatch=0, near_boundary=0, max_dp=0.0, p_bit_diff=0, count_diff=0)
+    for r in range(B):
+        n = int(exp["count"][r])
+        if int(got_cnt[r]) != n:
+            rep["count_diff"] += 1
+        m = min(n, got_dids.shape[1], exp["dist_ids"].shape[1])
+        gi, gp = got_dids[r, :m], got_dp[r, :m]
+        ei, ep = exp["dist_ids"][r, :m], exp["dist_p"][r, :m]
+        if not ordered:
+            o1, o2 = np.argsort(gi, kind="stable"), np.argsort(ei, kind="stable")
+            gi, gp, ei, ep = gi[o1], gp[o1], ei[o2], ep[o2]
+        if int(got_cnt[r]) == n:
+            assert np.array_equal(gi, ei), f"row {r}: distribution ids differ\n{gi[:16]}\n{ei[:16]}"
+            d = float(np.max(np.abs(gp.astype(np.float64) - ep.astype(np.float64)))) if m else 0.0
+            rep["max_dp"] = max(rep["max_dp"], d)
+            rep["p_bit_diff"] += int(np.count_nonzero(gp.view(np.uint32) != ep.view(np.uint32)))
+        if int(got_ids[r]) != int(exp["ids"][r]):
+            rep["id_mismatch"] += 1
+            ok = uniforms is not None and near_boundary(uniforms[r], exp["dist_p"][r, :n])
+            rep["near_boundary"] += int(ok)
+            assert ok, f"row {r}: sampled id {got_ids[r]} != {exp['ids'][r]} away from any CDF boundary"
+    assert rep["count_diff"] == 0, rep
+    assert rep["max_dp"] <= P_TOL, rep
+    return rep

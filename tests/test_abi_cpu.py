@@ -1,0 +1,50 @@
+"""CPU checks of the drop-in boundary: the library loads, exports every entry point the header declares, the
+Python binding table covers them all, and argument errors come back as status codes (no GPU needed)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+from qpack_b200 import _lib, build
+from qpack_b200.synth import PARAMS_DTYPE
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    inc = os.path.join(ROOT, "include")
+    for f in sorted(os.listdir(inc)):
+        if f.endswith(".h"):
+            names += re.findall(r"QPB_API[^;(]*?\b(qpb_\w+)\s*\(", open(os.path.join(inc, f)).read())
+    return names
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    build.build()
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 16
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/ but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert set(_lib.SIGNATURES) <= set(names)
+
+
+def test_parameter_block_layout_matches_reference_struct():
+    # qp::SamplerParams (include/qpack/engine.h:17-25): six 4-byte fields then a uint64 seed, 32 bytes
+    assert PARAMS_DTYPE.itemsize == 32
+    assert [PARAMS_DTYPE.fields[n][1] for n in PARAMS_DTYPE.names] == [0, 4, 8, 12, 16, 20, 24]
+
+
+def test_argument_errors_are_status_codes():
+    lib = _lib.load()
+    h = C.c_void_p()
+    assert lib.qpb_sampler_create(None, 0, 4) == _lib.ERR_INVALID
+    assert lib.qpb_sampler_create(C.byref(h), 0, 0) == _lib.ERR_INVALID
+    assert lib.qpb_sampler_destroy(None) == _lib.OK
+    assert lib.qpb_sampler_check(None, None) == _lib.ERR_INVALID
+    assert lib.qpb_sampler_set_params(None, None, 1) == _lib.ERR_INVALID
+    assert lib.qpb_sampler_last_error(None) == b"null handle"
+    assert lib.qpb_debug_expf(None, None, 0, None) == _lib.ERR_INVALID

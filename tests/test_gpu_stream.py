@@ -1,0 +1,225 @@
+"""GPU parity tests of the streaming kernel, through the C ABI, against the CPU checker and the fixtures
+generated from the reference.  Bit-exact ids, counts and distribution ids; probabilities within 1e-5 (and
+counted when not bit-identical)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import Oracle, make_params
+from qpack_b200 import synth
+from qpack_b200.sampler import BatchSampler, SamplerError, device_expf
+
+from helpers import compare_rows, small_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def run_device(params, logits, hist=None, hist_len=None, max_out=64, cluster=0, draw=True):
+    B = logits.shape[0]
+    bs = BatchSampler(B, 0)
+    bs.set_params(params)
+    bs.set_cluster(cluster)
+    d_logits = torch.from_numpy(np.ascontiguousarray(logits)).to(DEV)
+    d_hist = torch.from_numpy(np.ascontiguousarray(hist)).to(DEV) if hist is not None else None
+    d_hl = torch.from_numpy(np.ascontiguousarray(hist_len)).to(DEV) if hist_len is not None else None
+    ids, p, cnt, out = bs.dist(d_logits, d_hist, d_hl, max_out=max_out, draw=True)
+    bs.check()
+    res = (out.cpu().numpy(), cnt.cpu().numpy(), ids.cpu().numpy(), p.cpu().numpy())
+    bs.close()
+    return res
+
+
+def test_device_expf_is_the_c_librarys():
+    rng = np.random.default_rng(3)
+    x = np.concatenate([
+        rng.uniform(-110, 0, 1 << 20).astype(np.float32),
+        -np.abs(rng.standard_normal(1 << 18)).astype(np.float32) * 1e-3,
+        np.array([0.0, -0.0, -87.9, -88.0, -88.1, -103.0, -103.5, -103.9, -104.0, -200.0, -np.inf, -1e-30, -1e-45],
+                 np.float32),
+        np.linspace(-104.5, -102.5, 4001).astype(np.float32),
+    ])
+    got = device_expf(torch.from_numpy(x).to(DEV)).cpu().numpy()
+    want = Oracle.expf(x)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("cluster", [1, 2, 8])
+def test_small_fixture_cases(golden, cluster):
+    """Tiny, ragged and tie-heavy rows (V from 1 to 4099) with mixed parameters, incl. repeat_penalty < 1,
+    whole-history windows and out-of-range history ids."""
+    for i in range(int(golden["n_small"])):
+        x, hist, hl, p, ids, cnt, dids, dp = small_case(golden, i)
+        V = x.shape[1]
+        # rows whose candidate budget exceeds the streaming kernel's go to the whole-row kernel; both must agree
+        got = run_device(p, x, hist, hl, max_out=dids.shape[1], cluster=cluster)
+        rep = compare_rows(*got, dict(ids=ids, count=cnt, dist_ids=dids, dist_p=dp))
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (i, V, rep)
+
+
+def test_sampler_bench_row(golden):
+    """The reference micro-benchmark's row: ~152-way ties at the top, the index tie-break decides the set."""
+    x, h = synth.sampler_bench_row()
+    d_x = torch.from_numpy(x).to(DEV)
+    d_h = torch.from_numpy(h).to(DEV)
+    for k in range(4):
+        for cluster in (1, 4, 8):
+            bs = BatchSampler(1, 0)
+            bs.set_params(golden[f"sb{k}_params"])
+            bs.set_cluster(cluster)
+            ids, p, cnt = bs.dist(d_x, d_h, None, max_out=64)
+            n = int(cnt.item())
+            assert n == len(golden[f"sb{k}_dist_ids"])
+            assert np.array_equal(ids[0, :n].cpu().numpy(), golden[f"sb{k}_dist_ids"])
+            assert np.array_equal(p[0, :n].cpu().numpy().view(np.uint32), golden[f"sb{k}_dist_p"].view(np.uint32))
+            draws = [int(bs.sample(d_x, d_h).item()) for _ in range(8)]
+            bs.check()
+            assert draws == golden[f"sb{k}_draws"].tolist()
+            bs.close()
+
+
+def test_single_row_loop(golden):
+    """Config 1: one sampler, successive draws share one RNG stream (a draw with one survivor takes no word),
+    the sampled id is appended to the history."""
+    params, hist0 = synth.single_row_loop()
+    bs = BatchSampler(1, 0)
+    bs.set_params(params)
+    steps = len(golden["loop_ids"])
+    hist = torch.zeros((1, 64 + steps), dtype=torch.int32, device=DEV)
+    hist[0, :64] = torch.from_numpy(hist0).to(DEV)
+    got, counts = [], []
+    for step in range(steps):
+        lg = torch.from_numpy(synth.single_row_step(step)).to(DEV)
+        ids, p, cnt, out = bs.dist(lg, hist, 64 + step, max_out=64, draw=True)
+        hist[0, 64 + step] = out[0]
+        got.append(int(out.item()))
+        counts.append(int(cnt.item()))
+    bs.check()
+    assert got == golden["loop_ids"].tolist()
+    assert counts == golden["loop_counts"].tolist()
+    # resume from a saved RNG state: the next draws repeat
+    bs.close()
+
+
+def test_rng_state_get_set_resumes_stream():
+    wl = synth.serving_batch(rows=4)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    d_h = torch.from_numpy(wl.history).to(DEV)
+    bs = BatchSampler(4, 0)
+    bs.set_params(wl.params)
+    a = [bs.sample(d_x, d_h).cpu().numpy() for _ in range(3)]
+    st = [bs.rng_get(r) for r in range(4)]
+    b = [bs.sample(d_x, d_h).cpu().numpy() for _ in range(3)]
+    for r in range(4):
+        bs.rng_set(r, st[r])
+    c = [bs.sample(d_x, d_h).cpu().numpy() for _ in range(3)]
+    assert all(np.array_equal(x, y) for x, y in zip(b, c))
+    # and the stream equals the checker's: draws 1..6 of a per-row sampler
+    for r in range(4):
+        o = Oracle(wl.params[r:r + 1])
+        seq = [o.sample(wl.logits[r], wl.history[r]) for _ in range(6)]
+        assert seq == [int(v[r]) for v in a + b]
+    bs.close()
+
+
+@pytest.mark.parametrize("name,rows", [("serving", 96), ("sharded", 64)])
+@pytest.mark.parametrize("cluster", [0, 1, 4])
+def test_config_rows(name, rows, cluster):
+    wl = synth.serving_batch(rows=rows) if name == "serving" else synth.sharded_batch(rows=rows)
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    got = run_device(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64, cluster=cluster)
+    rep = compare_rows(*got, exp)
+    assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, rep
+
+
+def test_unaligned_rows_take_the_plain_load_path():
+    """Row stride and base not multiples of 16 bytes: the bulk-copy path is not usable, results are the same."""
+    wl = synth.serving_batch(rows=6, vocab=30001)
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    B, V = wl.logits.shape
+    buf = torch.zeros(B * (V + 3) + 1, dtype=torch.float32, device=DEV)
+    view = buf[1:].view(B, V + 3)[:, :V]
+    view.copy_(torch.from_numpy(wl.logits))
+    bs = BatchSampler(B, 0)
+    bs.set_params(wl.params)
+    for cluster in (1, 2, 8):
+        bs.set_params(wl.params)
+        bs.set_cluster(cluster)
+        ids, p, cnt, out = bs.dist(view, torch.from_numpy(wl.history).to(DEV), None, max_out=64, draw=True)
+        bs.check()
+        rep = compare_rows(out.cpu().numpy(), cnt.cpu().numpy(), ids.cpu().numpy(), p.cpu().numpy(), exp)
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0
+    bs.close()
+
+
+def test_vocab_sharded_emulated_on_one_gpu():
+    """Config 5 on one GPU: the G column shards are processed one after the other, their candidate lists
+    stacked as an all-gather would, then merged; ids equal the checker on the whole row."""
+    wl = synth.sharded_batch(rows=32)
+    exp = Oracle.sample_rows(wl.params, wl.logits, None, None, max_out=64)
+    B, V = wl.logits.shape
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    for G in (2, 4, 8):
+        per = V // G
+        assert per * G == V
+        bs = BatchSampler(B, 0)
+        bs.set_params(wl.params)
+        slots = bs.cand_slots(V, per)
+        assert slots == 64
+        parts = [bs.local_candidates(d_x[:, g * per:(g + 1) * per], V, g * per, slots) for g in range(G)]
+        allc = torch.stack(parts, 0).contiguous()
+        out, ids, p, cnt = bs.merge_sample(allc, V, max_out=64)
+        bs.check()
+        rep = compare_rows(out.cpu().numpy(), cnt.cpu().numpy(), ids.cpu().numpy(), p.cpu().numpy(), exp)
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0
+        bs.close()
+
+
+def test_host_buffer_entry_point():
+    wl = synth.serving_batch(rows=16)
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len)
+    bs = BatchSampler(16, 0)
+    bs.set_params(wl.params)
+    got = bs.sample_host(wl.logits, wl.history, wl.hist_len)
+    assert np.array_equal(got, exp["ids"])
+    bs.close()
+
+
+def test_errors_are_reported_not_thrown_across_the_boundary():
+    bs = BatchSampler(4, 0)
+    x = torch.zeros((8, 100), dtype=torch.float32, device=DEV)
+    with pytest.raises(SamplerError) as e:
+        bs.sample(x)  # parameters not set
+    assert e.value.code == 1
+    bs.set_params(make_params(1, seed=3))
+    with pytest.raises(SamplerError) as e:
+        bs.sample(x)  # more rows than the handle was created for
+    assert e.value.code == 1
+    bs.close()
+
+
+def test_full_size_batch_properties():
+    """B = 1024 at V = 151936 (the benchmark workload): ids do not depend on the cluster size, a second handle
+    with the same seeds repeats them, and greedy rows equal a stable argmax."""
+    wl = synth.serving_batch(rows=1024)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    d_h = torch.from_numpy(wl.history).to(DEV)
+    outs = []
+    for cluster in (1, 2, 1):
+        bs = BatchSampler(1024, 0)
+        bs.set_params(wl.params)
+        bs.set_cluster(cluster)
+        outs.append(bs.sample(d_x, d_h).cpu().numpy())
+        bs.check()
+        bs.close()
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len)
+    assert np.array_equal(outs[0], exp["ids"])
+    # greedy without penalty = first index of the maximum
+    p = make_params(1, temperature=0.0, repeat_penalty=1.0, seed=9)
+    bs = BatchSampler(1024, 0)
+    bs.set_params(p)
+    g = bs.sample(d_x).cpu().numpy()
+    bs.check()
+    bs.close()
+    assert np.array_equal(g, np.argmax(wl.logits, axis=1).astype(np.int32))
