@@ -104,6 +104,13 @@ QPB_API int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state
 /* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1, 2, 4 or 8. */
 QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
 
+/* Latency breakdown aid.  enable != 0 turns on per-row phase stamps (SM clock of the row's leader CTA:
+ * [0] start, [1] penalty set built, [2] row streamed, [3] exact candidate set, [4] cluster merge done,
+ * [5] candidates ordered, [6] softmax numerators, [7] end; [8] clocks spent in selects while streaming,
+ * [9] number of those selects, [10] candidates held at the end of the stream).  With h_clk != NULL the stamps
+ * of rows [0, n_rows) are copied out ([n_rows][16]).  enable == 0 turns them off again.  Synchronous. */
+QPB_API int qpb_sampler_phase_clocks(qpb_sampler *s, int enable, long long *h_clk, int n_rows);
+
 /* Number of kernels this handle has launched so far. */
 QPB_API int64_t qpb_sampler_launch_count(const qpb_sampler *s);
 

@@ -51,6 +51,56 @@ __device__ __forceinline__ int comp_id(unsigned long long c) { return (int)(0xff
 // ---- shared-memory barriers and bulk copies (non-multicast, own CTA only) ------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
+// Explicit shared-space accesses for the hot path (a pointer into dynamic shared memory that also serves
+// cluster-mapped accesses may otherwise be treated as generic).
+__device__ __forceinline__ int smem_atomic_add(int *p, int v) {
+  int old;
+  asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void smem_store_u64(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.shared.u64 [%0], %1;" ::"r"(smem_u32(p)), "l"(v) : "memory");
+}
+// 16-byte load from a 32-bit shared-space address
+__device__ __forceinline__ float4 lds_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+// mask |= BIT for every component of v that is not <= thr (NaN counts as "not <="): two instructions each
+template <int SHIFT>
+__device__ __forceinline__ void mask_not_le(const float4 &v, float thr, uint32_t &mask) {
+  asm("{\n\t.reg .pred p;\n\t"
+      "setp.gtu.f32 p, %1, %5;\n\t@p or.b32 %0, %0, %6;\n\t"
+      "setp.gtu.f32 p, %2, %5;\n\t@p or.b32 %0, %0, %7;\n\t"
+      "setp.gtu.f32 p, %3, %5;\n\t@p or.b32 %0, %0, %8;\n\t"
+      "setp.gtu.f32 p, %4, %5;\n\t@p or.b32 %0, %0, %9;\n\t}"
+      : "+r"(mask)
+      : "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w), "f"(thr), "n"(1u << SHIFT), "n"(2u << SHIFT), "n"(4u << SHIFT),
+        "n"(8u << SHIFT));
+}
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ float4 smem_load_f4(const float *p) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(p)));
+  return v;
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
@@ -100,7 +150,9 @@ __device__ __constant__ const unsigned long long kExp2Tab[32] = {
     0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
     0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
 
-__device__ __forceinline__ float expf_libm(float x) {
+// `tab` is the 32-entry table above, or a copy of it in shared memory (lanes index it with different values,
+// which the constant cache would serialise).
+__device__ __forceinline__ float expf_libm(float x, const unsigned long long *tab = kExp2Tab) {
   const uint32_t ux = __float_as_uint(x);
   const uint32_t abstop = (ux >> 20) & 0x7ffu;
   if (abstop >= 0x42bu) {  // |x| >= 88 or NaN
@@ -120,7 +172,7 @@ __device__ __forceinline__ float expf_libm(float x) {
   const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
   kd = __dsub_rn(kd, Shift);
   const double r = __fma_rn(InvLn2N, xd, -kd);
-  const unsigned long long t = kExp2Tab[ki & 31u] + (ki << 47);
+  const unsigned long long t = tab[ki & 31u] + (ki << 47);
   const double s = __longlong_as_double((long long)t);
   const double z = __fma_rn(C0, r, C1);
   const double r2 = __dmul_rn(r, r);
@@ -144,6 +196,33 @@ __device__ __forceinline__ unsigned long long mt_next(unsigned long long *mt, un
   unsigned long long x = mt[km] ^ (y >> 1) ^ ((y & 1ULL) ? 0xB5026F5AA96619E9ULL : 0ULL);
   mt[k] = x;
   *drawn = d + 1;
+  x ^= (x >> 29) & 0x5555555555555555ULL;
+  x ^= (x << 17) & 0x71D67FFFEDA60000ULL;
+  x ^= (x << 37) & 0xFFF7EEE000000000ULL;
+  x ^= x >> 43;
+  return x;
+}
+// The same step split in two so that the loads can be issued long before the word is needed.
+struct MtFetch {
+  unsigned long long a, b, c;  // mt[k], mt[k+1], mt[k+m]
+  unsigned int drawn;
+};
+__device__ __forceinline__ MtFetch mt_fetch(const unsigned long long *mt, const unsigned int *drawn) {
+  MtFetch f;
+  f.drawn = *drawn;
+  const int k = (int)(f.drawn % MT_N);
+  const int k1 = (k + 1 == MT_N) ? 0 : k + 1;
+  const int km = (k + MT_M >= MT_N) ? k + MT_M - MT_N : k + MT_M;
+  f.a = mt[k];
+  f.b = mt[k1];
+  f.c = mt[km];
+  return f;
+}
+__device__ __forceinline__ unsigned long long mt_commit(const MtFetch &f, unsigned long long *mt, unsigned int *drawn) {
+  const unsigned long long y = (f.a & 0xFFFFFFFF80000000ULL) | (f.b & 0x7FFFFFFFULL);
+  unsigned long long x = f.c ^ (y >> 1) ^ ((y & 1ULL) ? 0xB5026F5AA96619E9ULL : 0ULL);
+  mt[f.drawn % MT_N] = x;
+  *drawn = f.drawn + 1;
   x ^= (x >> 29) & 0x5555555555555555ULL;
   x ^= (x << 17) & 0x71D67FFFEDA60000ULL;
   x ^= (x << 37) & 0xFFF7EEE000000000ULL;

@@ -8,11 +8,12 @@
 //
 // How it maps to the B200: every f32 logit is read from HBM exactly once.  Each CTA streams its contiguous
 // slice of the row through a ring of shared-memory stages filled by bulk-async copies (cp.async.bulk +
-// mbarrier, no multicast), compares order-preserving keys against a running threshold and appends the few
-// survivors to a shared-memory candidate list; when the list fills, a radix select over the 64-bit
-// (key, ~index) composites keeps the best M and raises the threshold.  With more than one CTA per row the
-// per-CTA winners are pushed into the leader CTA's shared memory over DSMEM and selected once more.  The leader
-// then finishes the row on at most a few hundred candidates: penalty, rank sort, softmax, cut, draw.
+// mbarrier, no multicast), compares each float against a running threshold (one predicate per element) and
+// appends the few survivors to a shared-memory candidate list; when the list fills, a radix select over the
+// 64-bit (key, ~index) composites keeps the best M and raises the threshold.  With more than one CTA per row
+// the per-CTA winners are pushed into the leader CTA's shared memory over DSMEM and selected once more.  The
+// leader then finishes the row on at most a few hundred candidates: penalty, top-K select, rank sort, softmax,
+// cut, draw.
 #pragma once
 #include <cooperative_groups.h>
 
@@ -21,14 +22,21 @@
 namespace qpb {
 namespace cg = cooperative_groups;
 
-constexpr int kThreads = 256;        // threads per CTA
-constexpr int kTile = 2048;          // floats per ring stage (8 KB)
-constexpr int kStages = 4;           // ring depth: 32 KB in flight per CTA
-constexpr int kCandCap = 4096;       // candidate entries of the streaming phase (32 KB)
-constexpr int kCandHigh = kCandCap - kTile;  // select when the list grows beyond this
-constexpr int kMergeCap = kCandCap + kStages * kTile * 4 / 8;  // entries available to the cluster merge (ring reused)
-constexpr int kSmallMaxM = 768;      // rows with top_k + window above this take the whole-row kernel instead
+constexpr int kThreads = 256;                // threads per CTA
+constexpr int kTile = 4096;                  // floats per ring stage (16 KB)
+constexpr int kStages = 4;                   // ring depth: 64 KB in flight per CTA
+constexpr int kHalf = kTile / 2;             // a tile is scanned as two halves of 8 floats per thread
+constexpr int kCandCap = 3072;               // candidate entries of the streaming phase (24 KB)
+constexpr int kCandHigh = kCandCap - kHalf;  // careful mode: select when the list grows beyond this (a half adds <= kHalf)
+constexpr int kCandHighFast = 2048;          // fast mode: select after a tile that left more than this
+constexpr int kRingEntries = kStages * kTile * 4 / 8;
+constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to the cluster merge (ring reused)
+// Rows with top_k + window above this take the whole-row kernel instead.  It also bounds the "whole row" case of
+// top_m (M >= V/4 implies V <= 4 * 760 + 3 = 3043 <= kCandCap).
+constexpr int kSmallMaxM = 760;
 constexpr int kPenEmpty = -1;
+static_assert(kSmallMaxM <= kCandHigh && 4 * kSmallMaxM + 3 <= kCandCap, "candidate list sizing");
+static_assert(8 * kSmallMaxM <= kMergeCap, "cluster merge sizing");
 
 enum : int { MODE_SAMPLE = 0, MODE_LOCAL_TOPM = 1, MODE_MERGE = 2 };
 
@@ -60,12 +68,14 @@ struct StreamArgs {
   int cand_rows;           // row dimension of cand_io
   int pen_slots;           // penalty hash slots (power of two)
   int *status;
+  long long *phase_clk;    // optional [rows][16]: SM clock stamps of the leader CTA's phases (latency breakdown)
 };
 
 struct __align__(16) StreamSmem {
-  unsigned long long cand[kCandCap];        // candidates; the ring follows directly so that the merge can use both
+  unsigned long long cand[kCandCap];  // candidates; the ring follows directly so that the merge can use both
   float ring[kStages][kTile];
   uint64_t full[kStages];
+  unsigned long long exp_tab[32];
   uint32_t hist[256];
   uint32_t sel[4];
   int cand_count;
@@ -127,18 +137,10 @@ __device__ unsigned long long block_select_pivot(const unsigned long long *c, in
   for (int shift = 56; shift >= 0; shift -= 8) {
     hist[threadIdx.x] = 0;  // kThreads == 256
     __syncthreads();
-    for (int base = 0; base < n; base += kThreads) {  // uniform trip count: every lane takes part in the votes
-      const int i = base + threadIdx.x;
-      const unsigned long long v = i < n ? c[i] : 0ULL;
-      const bool in = i < n && (v & mask) == prefix;
-      // warp-aggregated histogram: lanes with the same digit elect one to add their count (tie-heavy rows
-      // would otherwise serialise on one shared-memory word)
-      const uint32_t digit = (uint32_t)(v >> shift) & 255u;
-      const uint32_t active = __ballot_sync(0xffffffffu, in);
-      if (in) {
-        const uint32_t peers = __match_any_sync(active, digit);
-        if ((peers & ((1u << lane) - 1u)) == 0) atomicAdd(&hist[digit], __popc(peers));
-      }
+#pragma unroll 4
+    for (int i = threadIdx.x; i < n; i += kThreads) {
+      const unsigned long long v = c[i];
+      if ((v & mask) == prefix) atomicAdd(&hist[(uint32_t)(v >> shift) & 255u], 1u);
     }
     __syncthreads();
     if (warp == 0) {
@@ -180,33 +182,48 @@ __device__ int block_compact(unsigned long long *c, int n, unsigned long long pi
   __syncthreads();
   for (int base = 0; base < n; base += PER * kThreads) {
     unsigned long long r[PER];
+    int mine = 0;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
       const int i = base + k * kThreads + threadIdx.x;
       r[k] = (i < n) ? c[i] : 0ULL;
+      if (r[k] < pivot) r[k] = 0ULL;  // composites are never 0
+      mine += r[k] != 0ULL;
     }
-    __syncthreads();  // every entry of this chunk is in registers before any slot below its end is rewritten
+    int incl = mine;  // warp scan of the per-lane keep counts, then one reservation per warp
 #pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      const bool keep = r[k] >= pivot && r[k] != 0ULL;
-      const uint32_t m = __ballot_sync(0xffffffffu, keep);
-      if (m) {
-        int basepos = 0;
-        if (lane == __ffs(m) - 1) basepos = atomicAdd(counter, __popc(m));
-        basepos = __shfl_sync(0xffffffffu, basepos, __ffs(m) - 1);
-        if (keep) c[basepos + __popc(m & ((1u << lane) - 1u))] = r[k];
-      }
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
     }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    __syncthreads();  // every entry of this chunk is in registers before any slot below its end is rewritten
+    int pos = 0;
+    if (lane == 31 && total > 0) pos = atomicAdd(counter, total);
+    pos = __shfl_sync(0xffffffffu, pos, 31) + incl - mine;
+#pragma unroll
+    for (int k = 0; k < PER; ++k)
+      if (r[k] != 0ULL) c[pos++] = r[k];
   }
   __syncthreads();
   return *counter;
 }
 
-// ---- the finish: penalty, order, softmax, cut, draw on n <= 4096 candidates (leader CTA) ------------------------
-// cand[0..n): exact M largest raw (key, id) composites, unordered.  `sorted` and `ev`/`pv` are shared-memory
-// areas that do not overlap cand[0..n) resp. each other: sorted: 4096 composites; ev, pv: 4096 floats each.
+// keep the `want` largest of c[0..n) at the front (no-op when n <= want); returns the new count
+__device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int want, uint32_t *hist, uint32_t *sel,
+                                              int *counter) {
+  if (n <= want) return n;
+  const unsigned long long pivot = block_select_pivot(c, n, want, hist, sel);
+  return block_compact(c, n, pivot, counter);
+}
+
+// ---- the finish: penalty, order, softmax, cut, draw (leader CTA) ----------------------------------------------
+// cand[0..n): a superset of the candidates the reference would hold, unordered (exactly its M largest raw
+// entries when the caller had to cut to M).  `sorted` (kCandCap composites) must not overlap cand; ev / pv
+// (kCandCap floats each) may alias cand, which is dead once `sorted` is written.
 __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
-                           const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv) {
+                           const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv,
+                           StreamSmem &S, const MtFetch &rng, long long *clk) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied
   if (npen > 0) {
@@ -222,15 +239,27 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     }
     __syncthreads();
   }
-  // order by (value desc, id asc) and keep the first K (sampler.cpp:43-44): rank = number of larger composites
-  const int nK = n < K ? n : K;
-  for (int i = threadIdx.x; i < n; i += kThreads) {
-    const unsigned long long c = cand[i];
-    int rank = 0;
-    for (int j = 0; j < n; ++j) rank += (cand[j] > c) ? 1 : 0;
-    if (rank < nK) sorted[rank] = c;
+  // the K best by (value desc, id asc) (sampler.cpp:43-44): select, then rank = number of larger composites
+  n = block_keep_top(cand, n, K, S.hist, S.sel, &S.cand_count);
+  const int nK = n;
+  {
+    // P lanes share one entry (P = 32, 16, 8, 4, 2 or 1, as many as the CTA can spare), each counting over a
+    // strided part of the list; partial ranks are summed with shuffles
+    int P = 32;
+    while (P > 1 && nK * P > kThreads) P >>= 1;
+    const int sub = threadIdx.x & (P - 1);
+    for (int i0 = 0; i0 < nK; i0 += kThreads / P) {
+      const int i = i0 + threadIdx.x / P;
+      const unsigned long long c = i < nK ? cand[i] : 0ULL;
+      int rank = 0;
+#pragma unroll 4
+      for (int j = sub; j < nK; j += P) rank += (cand[j] > c) ? 1 : 0;
+      for (int o = P >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+      if (i < nK && sub == 0) sorted[rank] = c;
+    }
   }
   __syncthreads();
+  if (clk) clk[5] = clock64();
 
   const bool greedy = p.temperature <= 0.f;
   if (greedy) {  // sampler.cpp:45; draw() of a one-entry distribution takes no random word (sampler.cpp:59)
@@ -246,13 +275,15 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   const float mx = key2f(comp_key(sorted[0]));
   for (int i = threadIdx.x; i < nK; i += kThreads) {
     const float v = key2f(comp_key(sorted[i]));
-    ev[i] = expf_libm(__fdiv_rn(__fsub_rn(v, mx), p.temperature));
+    ev[i] = expf_libm(__fdiv_rn(__fsub_rn(v, mx), p.temperature), S.exp_tab);
   }
   __syncthreads();
+  if (clk) clk[6] = clock64();
   if (warp != 0) return;
 
   // Ordered double arithmetic, replayed exactly: every lane of warp 0 carries the same running values.
   double sum = 0.0;
+#pragma unroll 8
   for (int j = 0; j < nK; ++j) sum += (double)ev[j];
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
   const bool use_minp = p.min_p > 0.f;
@@ -274,6 +305,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     }
   }
   double tot = 0.0;
+#pragma unroll 8
   for (int j = 0; j < keep; ++j) tot += (double)ev[j];  // sampler.cpp:54
   for (int j = lane; j < keep; j += 32) pv[j] = __double2float_rn(__ddiv_rn((double)ev[j], tot));  // :55
   __syncwarp();
@@ -281,7 +313,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   int pick = 0;
   if (keep > 1 && a.draw) {
     unsigned long long w = 0;
-    if (lane == 0) w = mt_next(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+    if (lane == 0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
     w = __shfl_sync(0xffffffffu, w, 0);
     double r = word_to_uniform(w);
     pick = keep - 1;
@@ -305,7 +337,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
   int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
@@ -319,6 +351,12 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
 
   const RowParams p = a.params[a.params_per_row ? row : 0];
   const int Vt = a.vocab_total;
+  long long *clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
+  long long select_clk = 0, wait_clk = 0, proc_clk = 0, sync_clk = 0;
+  int n_selects = 0;
+#define QPB_STAMP(k) do { if (clk) clk[k] = clock64(); } while (0)
+  QPB_STAMP(0);
+  if (clk) { clk[11] = 0; clk[12] = 0; clk[13] = 0; clk[14] = 0; }
 
   // this CTA's slice [s0, s1) of the local columns, cut at multiples of 4 floats to keep 16-byte alignment
   int per = (a.vocab + csize - 1) / csize;
@@ -333,20 +371,32 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
     mbar_fence_init();
     S.cand_count = 0;
   }
+  if (tid < 32) S.exp_tab[tid] = kExp2Tab[tid];
   __syncthreads();
 
   auto tile_len = [&](int t) { return min(kTile, s1 - s0 - t * kTile); };
   auto tile_bulk = [&](int t) { return base_aligned && ((tile_len(t) & 3) == 0); };
-  auto issue = [&](int t) {  // thread 0 only
+  // Ring slots are handed out by a running counter g: slot g uses stage g % kStages on phase (g / kStages) & 1.
+  auto issue = [&](int t, int g) {  // thread 0 only: tile t of the slice into ring slot g
     if (t < n_tiles && tile_bulk(t)) {
       const uint32_t bytes = (uint32_t)tile_len(t) * 4u;
-      uint64_t *bar = &S.full[t % kStages];
+      uint64_t *bar = &S.full[g % kStages];
       mbar_expect_tx(bar, bytes);
-      bulk_g2s(S.ring[t % kStages], rowp + s0 + (size_t)t * kTile, bytes, bar);
+      bulk_g2s(S.ring[g % kStages], rowp + s0 + (size_t)t * kTile, bytes, bar);
     }
   };
+  // Threshold bootstrap (long slices only): the first kStages copies fetch tiles spread over the slice as a
+  // sample; a value that at least `boot_rank` sampled columns reach becomes the first threshold, so that the
+  // stream itself only picks up about twice the M columns it needs instead of filling the list several times.
+  // It is a guess: if fewer than M columns pass, the slice is streamed again without it.
+  const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kStages;
   if (tid == 0)
-    for (int t = 0; t < kStages; ++t) issue(t);
+    for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, j);
+
+  // the three RNG state words this row's draw may need: loaded now, used at the very end
+  MtFetch rng = {};
+  if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw)
+    rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
 
   // penalty set and the candidate budget, while the first copies are in flight
   int npen = 0;
@@ -356,104 +406,286 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
     npen = build_pen_set(pen_tab, a.pen_slots, &S.pen_unique, a.history + (size_t)row * a.hist_stride, hn,
                          p.repeat_last_n, Vt, a.status);
   }
+  QPB_STAMP(1);
   const bool greedy = p.temperature <= 0.f;
   const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
   int M = min(Vt, K + npen);
   if (M >= Vt / 4) M = Vt;  // top_m returns the whole row in this case (sampler.cpp:14)
+  const int need = min(M, s1 - s0);  // columns this CTA must deliver
 
-  // ---- streaming phase ----
-  uint32_t thr = 0;  // accept keys strictly above; 0 accepts everything
+  // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
+  // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
+  // kernels_x86.cpp:509).  A NaN logit passes the test and is ordered below -inf by its key later.
+  float thr = __int_as_float(0x7fc00000);
   bool failed = false;
-  for (int t = 0; t < n_tiles; ++t) {
-    const int st = t % kStages;
-    const int len = tile_len(t);
-    const int tbase = s0 + t * kTile;
-    if (tile_bulk(t)) {
-      if (!mbar_wait_bounded(&S.full[st], (uint32_t)(t / kStages) & 1u)) failed = true;
-    } else {  // unaligned row or ragged tail: plain loads into the same stage
-      for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
-      __syncthreads();
-    }
-    uint32_t keys[8];
-    int nacc = 0;
+  int g0 = 0;  // ring slot of the slice's tile 0
+  bool booted = false;
+  if (can_boot) {
+    // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
+    const long long sample = (long long)kStages * kTile;
+    long long r = (9LL * M * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
+    r = r < 16 ? 16 : r;
+    booted = M < Vt && r <= 128;  // two maxima per thread hold the sample's best 128 well enough
+    for (int j = 0; j < kStages; ++j)
+      if (!mbar_wait_bounded(&S.full[j], 0u)) failed = true;
+    if (booted) {
+      float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
+      for (int j = 0; j < kStages; ++j) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int off = h * (kThreads * 4) + tid * 4;
-      const float4 v = *reinterpret_cast<const float4 *>(&S.ring[st][off]);
-      const float f[4] = {v.x, v.y, v.z, v.w};
+        for (int h = 0; h < kTile / (kThreads * 4); ++h) {
+          const float4 v = *reinterpret_cast<const float4 *>(&S.ring[j][h * kThreads * 4 + tid * 4]);
+          const float f4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t k = f2key(f[j]);
-        const bool acc = (off + j < len) && (k > thr);
-        keys[h * 4 + j] = acc ? k : 0u;
-        nacc += acc ? 1 : 0;
-      }
-    }
-    if (__any_sync(0xffffffffu, nacc > 0)) {
-      int incl = nacc;  // warp inclusive scan of the per-lane accept counts
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl += v;
-      }
-      const int total = __shfl_sync(0xffffffffu, incl, 31);
-      int wbase = 0;
-      if (lane == 0) wbase = atomicAdd(&S.cand_count, total);
-      wbase = __shfl_sync(0xffffffffu, wbase, 0);
-      int pos = wbase + incl - nacc;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (keys[e] != 0u) {
-          const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
-          if (pos < kCandCap) S.cand[pos] = make_comp(keys[e], (uint32_t)(a.id_offset + tbase + off));
-          ++pos;
+          for (int e = 0; e < 4; ++e) {
+            const float x = f4[e];  // NaN is ignored by fmaxf / fminf
+            m2 = fmaxf(m2, fminf(m1, x));
+            m1 = fmaxf(m1, x);
+          }
         }
       }
-    }
-    __syncthreads();  // stage consumed by every thread; candidate count settled
-    if (tid == 0) issue(t + kStages);
-    const int cnt = S.cand_count;
-    if (cnt > kCandCap) { if (tid == 0) atomicOr(a.status, ST_CAPACITY); }
-    if (cnt > kCandHigh && cnt > M) {
-      const int nn = min(cnt, kCandCap);
-      const unsigned long long pivot = block_select_pivot(S.cand, nn, M, S.hist, S.sel);
-      block_compact(S.cand, nn, pivot, &S.cand_count);
-      // later columns must beat the weakest kept key: an equal key at a higher index loses (sampler.cpp:16).
-      // The select may stop on a key prefix, so take the minimum over the kept entries.
-      uint32_t mk = 0xffffffffu;
-      for (int i = tid; i < M; i += kThreads) mk = min(mk, comp_key(S.cand[i]));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) mk = min(mk, __shfl_xor_sync(0xffffffffu, mk, o));
-      if (tid == 0) S.sel[3] = 0xffffffffu;
+      S.cand[2 * tid] = make_comp(f2key(m1), (uint32_t)(2 * tid));
+      S.cand[2 * tid + 1] = make_comp(f2key(m2), (uint32_t)(2 * tid + 1));
       __syncthreads();
-      if (lane == 0) atomicMin(&S.sel[3], mk);
+      const unsigned long long pivot = block_select_pivot(S.cand, 2 * kThreads, (int)r, S.hist, S.sel);
+      thr = key2f((uint32_t)(pivot >> 32));  // a lower bound of the r-th largest; key 0 gives NaN = no threshold
+    } else {
       __syncthreads();
-      thr = S.sel[3];
     }
+    if (clk) clk[15] = clock64() - clk[1];
+    // the sample has been read by every thread: start the stream proper (tile 0 is fetched again with the rest)
+    g0 = kStages;
+    if (tid == 0)
+      for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
   }
+
+  // keep the M best of the list and raise the threshold to the weakest of them; all threads call it
+  auto shrink = [&]() {
+    const long long c0 = clk ? clock64() : 0;
+    block_keep_top(S.cand, min(S.cand_count, kCandCap), M, S.hist, S.sel, &S.cand_count);
+    // later columns must beat the weakest kept key: an equal key at a higher index loses.  The select may stop
+    // on a key prefix, so take the minimum over the kept entries.
+    uint32_t mk = 0xffffffffu;
+    for (int i = tid; i < M; i += kThreads) mk = min(mk, comp_key(S.cand[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mk = min(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+    if (tid == 0) S.sel[3] = 0xffffffffu;
+    __syncthreads();
+    if (lane == 0) atomicMin(&S.sel[3], mk);
+    __syncthreads();
+    thr = key2f(S.sel[3]);  // key 1 (a NaN is among the kept) maps back to NaN: keep taking everything
+    if (clk) { select_clk += clock64() - c0; ++n_selects; }
+  };
+
+  // ---- streaming phase ----
+  // Fast mode scans a whole tile between two barriers and expects a handful of survivors.  Careful mode (no
+  // threshold yet, or a tile that overflowed the list in fast mode) scans half a tile at a time and selects
+  // whenever another half might not fit, so the list can never overflow whatever the data.
+  const uint32_t ring_s = smem_u32(&S.ring[0][0]), full_s = smem_u32(&S.full[0]);
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    bool careful = false;
+    for (int t = 0; t < n_tiles;) {
+      const int g = g0 + t;
+      const int st = g % kStages;
+      const int len = tile_len(t);
+      const int tbase = s0 + t * kTile;
+      if (!careful && thr == thr && len == kTile && base_aligned) {
+        // ---- fast tile: full, bulk-copied, threshold known.  Kept to a minimum of instructions: the scan is
+        // issue-latency bound with 8 warps per CTA. ----
+        const uint32_t bar = full_s + (uint32_t)st * 8u;
+        const uint32_t par = (uint32_t)(g / kStages) & 1u;
+        for (int polls = 0; !mbar_try_wait_addr(bar, par);)
+          if (++polls > (1 << 22)) { failed = true; break; }
+        const int cnt_before = S.cand_count;
+        const uint32_t stage_s = ring_s + (uint32_t)st * (kTile * 4u);
+        const uint32_t lane_s = stage_s + (uint32_t)tid * 16u;
+        uint32_t mask = 0;  // bit 4c + j: column c * 1024 + tid * 4 + j of the tile survives
+        mask_not_le<0>(lds_f4(lane_s), thr, mask);
+        mask_not_le<4>(lds_f4(lane_s + 4096u), thr, mask);
+        mask_not_le<8>(lds_f4(lane_s + 8192u), thr, mask);
+        mask_not_le<12>(lds_f4(lane_s + 12288u), thr, mask);
+        const uint32_t lanes = __ballot_sync(0xffffffffu, mask != 0u);
+        if (lanes != 0u) {
+          // Same-address shared-memory atomics serialise and a warp scan is not free either: a warp with few
+          // survivors lets each of those lanes reserve its own slots, a warp with many reserves once for all of
+          // them.  Survivors are re-read from the stage by position so that only they cost instructions.
+          const int nacc = __popc(mask);
+          int pos;
+          if (__popc(lanes) <= 6) {
+            pos = nacc ? smem_atomic_add(&S.cand_count, nacc) : 0;
+          } else {
+            int incl = nacc;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const int v = __shfl_up_sync(0xffffffffu, incl, o);
+              if (lane >= o) incl += v;
+            }
+            int wbase = 0;
+            if (lane == 31) wbase = smem_atomic_add(&S.cand_count, incl);
+            pos = __shfl_sync(0xffffffffu, wbase, 31) + incl - nacc;
+          }
+          while (mask) {
+            const int e = __ffs(mask) - 1;
+            mask &= mask - 1u;
+            const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
+            if (pos < kCandCap)
+              smem_store_u64(&S.cand[pos], make_comp(f2key(lds_f32(stage_s + (uint32_t)off * 4u)), (uint32_t)(a.id_offset + tbase + off)));
+            ++pos;
+          }
+        }
+        __syncthreads();  // stage consumed by every thread; candidate count settled
+        const int cnt = S.cand_count;
+        if (cnt > kCandCap) {
+          // more survivors than the list holds: forget this tile's, scan it again half by half
+          __syncthreads();
+          if (tid == 0) S.cand_count = cnt_before;
+          careful = true;
+          if (cnt_before > kCandHigh && cnt_before > M) { __syncthreads(); shrink(); }
+          __syncthreads();
+          continue;
+        }
+        if (tid == 0) issue(t + kStages, g + kStages);
+        if (cnt > kCandHighFast && cnt > M) shrink();
+        ++t;
+        continue;
+      }
+      const long long w0 = clk ? clock64() : 0;
+      if (tile_bulk(t)) {
+        if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g / kStages) & 1u)) failed = true;
+      } else {  // unaligned row or ragged tail: plain loads into the same stage
+        for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
+        __syncthreads();
+      }
+      const long long w1 = clk ? clock64() : 0;
+      const int cnt_before = S.cand_count;  // settled: the previous tile ended with a barrier
+      const bool slow = careful || thr != thr;
+      for (int half = 0; half < 2; ++half) {
+        const int hlen = min(kHalf, len - half * kHalf);  // columns of this half (uniform)
+        if (hlen <= 0) break;
+        const float *src = &S.ring[st][half * kHalf];
+        const float4 v0 = smem_load_f4(src + tid * 4);
+        const float4 v1 = smem_load_f4(src + kThreads * 4 + tid * 4);
+        const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+        const int hbase = a.id_offset + tbase + half * kHalf;  // global id of the half's first column
+        if (thr != thr) {
+          // no threshold yet: the whole half is taken, every column has its own slot, no atomics
+          const int cbase = S.cand_count;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
+            if (off < hlen && cbase + off < kCandCap) S.cand[cbase + off] = make_comp(f2key(f[e]), (uint32_t)(hbase + off));
+          }
+          __syncthreads();
+          if (tid == 0) S.cand_count = cbase + hlen;
+        } else {
+          // one predicate per column; the bits of a ragged last half are masked by position
+          uint32_t accmask = 0;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) accmask |= !(f[e] <= thr) ? (1u << e) : 0u;
+          if (hlen != kHalf) {
+            const int n0 = min(4, max(0, hlen - tid * 4)), n1 = min(4, max(0, hlen - kThreads * 4 - tid * 4));
+            accmask &= ((1u << n0) - 1u) | (((1u << n1) - 1u) << 4);
+          }
+          const uint32_t lanes = __ballot_sync(0xffffffffu, accmask != 0u);
+          if (lanes != 0u) {
+            // Same-address shared-memory atomics serialise and warp votes are not free either: a warp with few
+            // survivors lets each of those lanes reserve its own slots, a warp with many reserves once for all
+            // of them and places them by a scan of the per-lane counts.  Survivors are re-read from the stage by
+            // position so that only they cost instructions.
+            const int nacc = __popc(accmask);
+            int pos;
+            if (__popc(lanes) <= 6) {
+              pos = nacc ? smem_atomic_add(&S.cand_count, nacc) : 0;
+            } else {
+              int incl = nacc;
+#pragma unroll
+              for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+              }
+              int wbase = 0;
+              if (lane == 31) wbase = smem_atomic_add(&S.cand_count, incl);
+              pos = __shfl_sync(0xffffffffu, wbase, 31) + incl - nacc;
+            }
+            while (accmask) {
+              const int e = __ffs(accmask) - 1;
+              accmask &= accmask - 1u;
+              const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
+              if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(src[off]), (uint32_t)(hbase + off)));
+              ++pos;
+            }
+          }
+        }
+        if (slow) {
+          __syncthreads();
+          const int c = S.cand_count;
+          if (c > kCandCap && tid == 0) atomicOr(a.status, ST_CAPACITY);  // cannot happen: c <= kCandHigh + kHalf
+          if (c > kCandHigh && c > M) shrink();
+        }
+      }
+      const long long w2 = clk ? clock64() : 0;
+      __syncthreads();  // stage consumed by every thread; candidate count settled
+      if (clk) { const long long w3 = clock64(); wait_clk += w1 - w0; proc_clk += w2 - w1; sync_clk += w3 - w2; }
+      const int cnt = S.cand_count;
+      if (!slow && cnt > kCandCap) {
+        // more survivors than the list holds: forget this tile's, scan it again half by half
+        __syncthreads();
+        if (tid == 0) S.cand_count = cnt_before;
+        careful = true;
+        if (cnt_before > kCandHigh && cnt_before > M) { __syncthreads(); shrink(); }
+        __syncthreads();
+        continue;
+      }
+      if (tid == 0) issue(t + kStages, g + kStages);
+      if (!slow && cnt > kCandHighFast && cnt > M) shrink();
+      ++t;
+    }
+    // every column above the bootstrap threshold was collected; with at least `need` of them the needed ones
+    // are all in the list.  Otherwise the guess was too high: stream the slice once more from "no threshold".
+    if (!booted || S.cand_count >= need) break;
+    __syncthreads();
+    booted = false;
+    thr = __int_as_float(0x7fc00000);
+    g0 += n_tiles;
+    if (tid == 0) {
+      S.cand_count = 0;
+      for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+    }
+    if (clk) clk[14] += 1;
+    __syncthreads();
+  }
+  QPB_STAMP(2);
+  if (clk) { clk[8] = select_clk; clk[9] = n_selects; clk[10] = S.cand_count; clk[11] = wait_clk; clk[12] = proc_clk; clk[13] = sync_clk; }
   if (failed && tid == 0) atomicOr(a.status, ST_COPY_TIMEOUT);
 
   // MODE_MERGE: candidates come from the gathered per-shard lists instead of a stream
   if (MODE == MODE_MERGE) {
     const int total = a.n_shards * a.cand_slots;
-    for (int i = tid; i < total; i += kThreads) {
-      const int sh = i / a.cand_slots, s = i - sh * a.cand_slots;
-      const unsigned long long c = a.cand_io[((size_t)sh * a.cand_rows + row) * a.cand_slots + s];
-      if (c != 0ULL) {
-        const int pos = atomicAdd(&S.cand_count, 1);
-        if (pos < kMergeCap) S.cand[pos] = c;
+    for (int i0 = 0; i0 < total; i0 += kThreads) {  // uniform trip count: every lane votes
+      const int i = i0 + tid;
+      unsigned long long c = 0ULL;
+      if (i < total) {
+        const int sh = i / a.cand_slots, s = i - sh * a.cand_slots;
+        c = a.cand_io[((size_t)sh * a.cand_rows + row) * a.cand_slots + s];
       }
+      const uint32_t m = __ballot_sync(0xffffffffu, c != 0ULL);
+      int wbase = 0;
+      if (lane == 0 && m) wbase = atomicAdd(&S.cand_count, __popc(m));
+      wbase = __shfl_sync(0xffffffffu, wbase, 0);
+      const int pos = wbase + __popc(m & ((1u << lane) - 1u));
+      if (c != 0ULL && pos < kMergeCap) S.cand[pos] = c;
     }
     __syncthreads();
     if (S.cand_count > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
   }
 
-  // ---- exact top-M of this CTA ----
   int n = min(S.cand_count, MODE == MODE_MERGE ? kMergeCap : kCandCap);
-  if (n > M) {
-    const unsigned long long pivot = block_select_pivot(S.cand, n, M, S.hist, S.sel);
-    n = block_compact(S.cand, n, pivot, &S.cand_count);
-  }
+  // The reference penalises exactly its M largest raw entries.  When the penalty only lowers values
+  // (repeat_penalty >= 1) the K best after the penalty are the same over any superset of those M, so the exact
+  // raw cut can be skipped; a penalty below 1 raises values and needs it.  Lists that travel (cluster merge,
+  // all-gather) are always cut to M to bound their size.
+  const bool exact_m = (npen > 0 && !(p.repeat_penalty >= 1.f)) || csize > 1 || MODE != MODE_SAMPLE;
+  if (exact_m) n = block_keep_top(S.cand, n, M, S.hist, S.sel, &S.cand_count);
+  QPB_STAMP(3);
 
   // ---- cluster merge: every CTA pushes its winners into the leader's list over DSMEM ----
   if (csize > 1) {
@@ -470,11 +702,9 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
     cluster.sync();
     if (crank != 0) return;
     n = min(S.cand_count, kMergeCap);
-    if (n > M) {
-      const unsigned long long pivot = block_select_pivot(S.cand, n, M, S.hist, S.sel);
-      n = block_compact(S.cand, n, pivot, &S.cand_count);
-    }
+    n = block_keep_top(S.cand, n, M, S.hist, S.sel, &S.cand_count);
   }
+  QPB_STAMP(4);
 
   if (MODE == MODE_LOCAL_TOPM) {  // hand this GPU's winners to the all-gather
     unsigned long long *out = a.cand_io + (size_t)row * a.cand_slots;
@@ -486,8 +716,9 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
   unsigned long long *sorted = reinterpret_cast<unsigned long long *>(&S.ring[0][0]);
   float *ev = reinterpret_cast<float *>(&S.cand[0]);
   float *pv = ev + kCandCap;
-  // finish_row reads cand[0..n) until the rank sort is done, then overwrites it with ev / pv (n <= 4096)
-  finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv);
+  finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, rng, clk);
+  QPB_STAMP(7);
+#undef QPB_STAMP
 }
 
 }  // namespace qpb

@@ -42,6 +42,7 @@ struct qpb_sampler {
   int *d_stage_hlen = nullptr;
   int *d_stage_ids = nullptr;
   cudaStream_t own_stream = nullptr;
+  long long *d_phase_clk = nullptr;  // [max_rows][16] when phase stamps are enabled
   std::string err;
 };
 
@@ -190,6 +191,7 @@ void fill_common(qpb_sampler *s, const Inputs &in, StreamArgs &a) {
   a.rng_drawn = s->d_drawn;
   a.status = s->d_status;
   a.pen_slots = pen_slots_for(s->max_window);
+  a.phase_clk = s->d_phase_clk;
 }
 
 // rows whose candidate budget exceeds the streaming kernel's take the whole-row kernel
@@ -277,6 +279,7 @@ int qpb_sampler_destroy(qpb_sampler *s) {
   cudaFree(s->d_stage_hist);
   cudaFree(s->d_stage_hlen);
   cudaFree(s->d_stage_ids);
+  cudaFree(s->d_phase_clk);
   whole_free(s);
   if (s->own_stream) cudaStreamDestroy(s->own_stream);
   delete s;
@@ -414,6 +417,26 @@ int qpb_sampler_set_cluster(qpb_sampler *s, int cluster) {
   if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8)
     return fail(s, QPB_ERR_INVALID, "cluster must be 0, 1, 2, 4 or 8");
   s->cluster = cluster;
+  return QPB_OK;
+}
+
+int qpb_sampler_phase_clocks(qpb_sampler *s, int enable, long long *h_clk, int n_rows) {
+  if (!s) return QPB_ERR_INVALID;
+  DeviceGuard g(s->device);
+  if (enable && !s->d_phase_clk) {
+    QPB_CUDA(s, cudaMalloc(&s->d_phase_clk, sizeof(long long) * 16 * (size_t)s->max_rows));
+    QPB_CUDA(s, cudaMemset(s->d_phase_clk, 0, sizeof(long long) * 16 * (size_t)s->max_rows));
+  }
+  if (h_clk && s->d_phase_clk) {
+    if (n_rows < 1 || n_rows > s->max_rows) return fail(s, QPB_ERR_INVALID, "n_rows outside [1, max_rows]");
+    QPB_CUDA(s, cudaDeviceSynchronize());
+    QPB_CUDA(s, cudaMemcpy(h_clk, s->d_phase_clk, sizeof(long long) * 16 * (size_t)n_rows, cudaMemcpyDeviceToHost));
+  }
+  if (!enable && s->d_phase_clk) {
+    QPB_CUDA(s, cudaDeviceSynchronize());
+    cudaFree(s->d_phase_clk);
+    s->d_phase_clk = nullptr;
+  }
   return QPB_OK;
 }
 

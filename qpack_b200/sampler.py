@@ -160,6 +160,12 @@ class BatchSampler:
         assert st.shape == (313,)
         self._ck(self._lib.qpb_sampler_rng_set(self._h, int(row), st.ctypes.data))
 
+    def phase_clocks(self, enable: bool = True, rows: int = 0) -> Optional[np.ndarray]:
+        """Turns the per-row phase stamps on/off; with rows > 0 returns them as int64 [rows, 16]."""
+        out = np.zeros((rows, 16), np.int64) if rows > 0 else None
+        self._ck(self._lib.qpb_sampler_phase_clocks(self._h, int(enable), out.ctypes.data if rows > 0 else None, rows))
+        return out
+
     @property
     def launches(self) -> int:
         return int(self._lib.qpb_sampler_launch_count(self._h))
