@@ -101,7 +101,7 @@ QPB_API int qpb_sampler_check(qpb_sampler *s, void *stream);
 QPB_API int qpb_sampler_rng_get(qpb_sampler *s, int row, uint64_t *h_state313);
 QPB_API int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state313);
 
-/* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1, 2, 4 or 8. */
+/* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1 to 8. */
 QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
 
 /* Latency breakdown aid.  enable != 0 turns on per-row phase stamps (SM clock of the row's leader CTA:

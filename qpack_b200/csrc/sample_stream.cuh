@@ -24,16 +24,16 @@ namespace cg = cooperative_groups;
 
 constexpr int kThreads = 256;                // threads per CTA
 constexpr int kTile = 4096;                  // floats per ring stage (16 KB)
-constexpr int kStages = 4;                   // ring depth: 64 KB in flight per CTA
+constexpr int kStages = 3;                   // ring depth: 48 KB in flight per CTA
 constexpr int kHalf = kTile / 2;             // a tile is scanned as two halves of 8 floats per thread
-constexpr int kCandCap = 3072;               // candidate entries of the streaming phase (24 KB)
+constexpr int kCandCap = 2816;               // candidate entries of the streaming phase (22 KB)
 constexpr int kCandHigh = kCandCap - kHalf;  // careful mode: select when the list grows beyond this (a half adds <= kHalf)
-constexpr int kCandHighFast = 2048;          // fast mode: select after a tile that left more than this
+constexpr int kCandHighFast = 1792;          // fast mode: select after a tile that left more than this
 constexpr int kRingEntries = kStages * kTile * 4 / 8;
 constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to the cluster merge (ring reused)
 // Rows with top_k + window above this take the whole-row kernel instead.  It also bounds the "whole row" case of
-// top_m (M >= V/4 implies V <= 4 * 760 + 3 = 3043 <= kCandCap).
-constexpr int kSmallMaxM = 760;
+// top_m (M >= V/4 implies V <= 4 * 700 + 3 = 2803 <= kCandCap).
+constexpr int kSmallMaxM = 700;
 constexpr int kPenEmpty = -1;
 static_assert(kSmallMaxM <= kCandHigh && 4 * kSmallMaxM + 3 <= kCandCap, "candidate list sizing");
 static_assert(8 * kSmallMaxM <= kMergeCap, "cluster merge sizing");
@@ -98,29 +98,32 @@ __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) 
   return false;
 }
 
-// returns the number of distinct ids; all threads of the CTA call it
-__device__ int build_pen_set(int *tab, int slots, int *unique_ctr, const int *hist, long long hn, int last_n,
-                             int vocab_total, int *status) {
+// Part 1 (no barrier): clears the table and fetches this thread's first id of the window, so that the global
+// load is in flight while other work goes on.  window = [from, hn) of hist.
+__device__ __forceinline__ int pen_prefetch(int *tab, int slots, int *unique_ctr, const int *hist, long long from,
+                                            long long hn) {
   for (int i = threadIdx.x; i < slots; i += kThreads) tab[i] = kPenEmpty;
   if (threadIdx.x == 0) *unique_ctr = 0;
-  __syncthreads();
-  // "hn > (size_t)repeat_last_n ? hn - repeat_last_n : 0": a negative repeat_last_n means the whole history
-  long long from = 0;
-  if (last_n >= 0 && hn > (long long)last_n) from = hn - last_n;
-  int mine = 0;
-  for (long long i = from + threadIdx.x; i < hn; i += kThreads) {
-    const int t = hist[i];
-    if (t < 0 || t >= vocab_total) continue;
-    uint32_t h = pen_hash(t, slots);
-    int probe = 0;
-    for (; probe < slots; ++probe) {
-      const int old = atomicCAS(&tab[h], kPenEmpty, t);
-      if (old == kPenEmpty) { ++mine; break; }
-      if (old == t) break;
-      h = (h + 1) & (uint32_t)(slots - 1);
-    }
-    if (probe == slots) atomicOr(status, ST_PEN_TABLE_FULL);
+  return (from + threadIdx.x < hn) ? hist[from + threadIdx.x] : -1;
+}
+__device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_total, int *status) {
+  if (t < 0 || t >= vocab_total) return 0;  // out-of-range ids are skipped (sampler.cpp:36)
+  uint32_t h = pen_hash(t, slots);
+  for (int probe = 0; probe < slots; ++probe) {
+    const int old = atomicCAS(&tab[h], kPenEmpty, t);
+    if (old == kPenEmpty) return 1;
+    if (old == t) return 0;
+    h = (h + 1) & (uint32_t)(slots - 1);
   }
+  atomicOr(status, ST_PEN_TABLE_FULL);
+  return 0;
+}
+// Part 2 (a barrier must separate it from part 1): inserts the window, returns the number of distinct ids.
+__device__ int pen_build(int *tab, int slots, int *unique_ctr, const int *hist, long long from, long long hn,
+                         int first_id, int vocab_total, int *status) {
+  int mine = pen_insert(tab, slots, first_id, vocab_total, status);
+  for (long long i = from + kThreads + threadIdx.x; i < hn; i += kThreads)
+    mine += pen_insert(tab, slots, hist[i], vocab_total, status);
   if (mine) atomicAdd(unique_ctr, mine);
   __syncthreads();
   return *unique_ctr;
@@ -134,19 +137,19 @@ __device__ unsigned long long block_select_pivot(const unsigned long long *c, in
   unsigned long long prefix = 0, mask = 0;
   uint32_t need = (uint32_t)want;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  hist[threadIdx.x] = 0;  // kThreads == 256
+  __syncthreads();
   for (int shift = 56; shift >= 0; shift -= 8) {
-    hist[threadIdx.x] = 0;  // kThreads == 256
-    __syncthreads();
 #pragma unroll 4
     for (int i = threadIdx.x; i < n; i += kThreads) {
       const unsigned long long v = c[i];
       if ((v & mask) == prefix) atomicAdd(&hist[(uint32_t)(v >> shift) & 255u], 1u);
     }
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 0) {  // lane l owns bins 8l .. 8l+7: reads them, clears them for the next pass
       uint32_t loc[8], s = 0;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) { loc[k] = hist[8 * lane + k]; s += loc[k]; }
+      for (int k = 0; k < 8; ++k) { loc[k] = hist[8 * lane + k]; s += loc[k]; hist[8 * lane + k] = 0; }
       uint32_t suf = s;  // inclusive suffix sum over lanes >= lane
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -170,7 +173,6 @@ __device__ unsigned long long block_select_pivot(const unsigned long long *c, in
     mask |= 0xffULL << shift;
     if (need == bucket) break;
   }
-  __syncthreads();
   return prefix;
 }
 
@@ -337,7 +339,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
   int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
@@ -349,7 +351,10 @@ __global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_c
   const int row = a.row_list ? a.row_list[slot] : slot;
   const int tid = threadIdx.x, lane = tid & 31;
 
+  // independent global loads first, so that their latencies overlap
   const RowParams p = a.params[a.params_per_row ? row : 0];
+  long long hn = (a.history == nullptr) ? 0 : (a.hist_len ? a.hist_len[row] : a.hist_len_all);
+  const bool want_rng = MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw;
   const int Vt = a.vocab_total;
   long long *clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
   long long select_clk = 0, wait_clk = 0, proc_clk = 0, sync_clk = 0;
@@ -386,32 +391,26 @@ __global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_c
     }
   };
   // Threshold bootstrap (long slices only): the first kStages copies fetch tiles spread over the slice as a
-  // sample; a value that at least `boot_rank` sampled columns reach becomes the first threshold, so that the
-  // stream itself only picks up about twice the M columns it needs instead of filling the list several times.
-  // It is a guess: if fewer than M columns pass, the slice is streamed again without it.
+  // sample; a value that a chosen number of sampled columns reach becomes the first threshold, so that the stream
+  // itself only picks up about twice the M columns it needs instead of filling the list several times.  It is a
+  // guess: if fewer than M columns pass, the slice is streamed again without it.
   const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kStages;
   if (tid == 0)
     for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, j);
 
   // the three RNG state words this row's draw may need: loaded now, used at the very end
   MtFetch rng = {};
-  if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw)
-    rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+  if (want_rng) rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
 
-  // penalty set and the candidate budget, while the first copies are in flight
-  int npen = 0;
-  if (p.repeat_penalty != 1.f && a.history != nullptr) {
-    long long hn = a.hist_len ? a.hist_len[row] : a.hist_len_all;
-    hn = hn < 0 ? 0 : (hn > a.hist_stride ? a.hist_stride : hn);
-    npen = build_pen_set(pen_tab, a.pen_slots, &S.pen_unique, a.history + (size_t)row * a.hist_stride, hn,
-                         p.repeat_last_n, Vt, a.status);
-  }
-  QPB_STAMP(1);
-  const bool greedy = p.temperature <= 0.f;
-  const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
-  int M = min(Vt, K + npen);
-  if (M >= Vt / 4) M = Vt;  // top_m returns the whole row in this case (sampler.cpp:14)
-  const int need = min(M, s1 - s0);  // columns this CTA must deliver
+  // history window (sampler.cpp:32-35): "hn > (size_t)repeat_last_n ? hn - repeat_last_n : 0", so a negative
+  // repeat_last_n means the whole history.  The ids are fetched now and inserted after the sample scan.
+  const bool use_pen = p.repeat_penalty != 1.f && a.history != nullptr;
+  hn = hn < 0 ? 0 : (hn > a.hist_stride ? a.hist_stride : hn);
+  long long hfrom = 0;
+  if (p.repeat_last_n >= 0 && hn > (long long)p.repeat_last_n) hfrom = hn - p.repeat_last_n;
+  const int *hrow = a.history + (size_t)row * a.hist_stride;
+  int first_id = -1;
+  if (use_pen) first_id = pen_prefetch(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn);
 
   // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
   // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
@@ -419,6 +418,36 @@ __global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_c
   float thr = __int_as_float(0x7fc00000);
   bool failed = false;
   int g0 = 0;  // ring slot of the slice's tile 0
+  float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
+  if (can_boot) {
+    for (int j = 0; j < kStages; ++j) {
+      if (!mbar_wait_bounded(&S.full[j], 0u)) failed = true;
+#pragma unroll
+      for (int h = 0; h < kTile / (kThreads * 4); ++h) {
+        const float4 v = *reinterpret_cast<const float4 *>(&S.ring[j][h * kThreads * 4 + tid * 4]);
+        const float f4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float x = f4[e];  // NaN is ignored by fmaxf / fminf
+          m2 = fmaxf(m2, fminf(m1, x));
+          m1 = fmaxf(m1, x);
+        }
+      }
+    }
+  }
+  __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
+  if (can_boot) {   // start the stream proper while the threshold is worked out (tile 0 is fetched again)
+    g0 = kStages;
+    if (tid == 0)
+      for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+  }
+  const int npen = use_pen ? pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status) : 0;
+  QPB_STAMP(1);
+  const bool greedy = p.temperature <= 0.f;
+  const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
+  int M = min(Vt, K + npen);
+  if (M >= Vt / 4) M = Vt;  // top_m returns the whole row in this case (sampler.cpp:14)
+  const int need = min(M, s1 - s0);  // columns this CTA must deliver
   bool booted = false;
   if (can_boot) {
     // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
@@ -426,36 +455,15 @@ __global__ void __launch_bounds__(kThreads, 2) stream_rows_kernel(const __grid_c
     long long r = (9LL * M * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
     r = r < 16 ? 16 : r;
     booted = M < Vt && r <= 128;  // two maxima per thread hold the sample's best 128 well enough
-    for (int j = 0; j < kStages; ++j)
-      if (!mbar_wait_bounded(&S.full[j], 0u)) failed = true;
     if (booted) {
-      float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
-      for (int j = 0; j < kStages; ++j) {
-#pragma unroll
-        for (int h = 0; h < kTile / (kThreads * 4); ++h) {
-          const float4 v = *reinterpret_cast<const float4 *>(&S.ring[j][h * kThreads * 4 + tid * 4]);
-          const float f4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float x = f4[e];  // NaN is ignored by fmaxf / fminf
-            m2 = fmaxf(m2, fminf(m1, x));
-            m1 = fmaxf(m1, x);
-          }
-        }
-      }
       S.cand[2 * tid] = make_comp(f2key(m1), (uint32_t)(2 * tid));
       S.cand[2 * tid + 1] = make_comp(f2key(m2), (uint32_t)(2 * tid + 1));
       __syncthreads();
       const unsigned long long pivot = block_select_pivot(S.cand, 2 * kThreads, (int)r, S.hist, S.sel);
       thr = key2f((uint32_t)(pivot >> 32));  // a lower bound of the r-th largest; key 0 gives NaN = no threshold
-    } else {
-      __syncthreads();
+      __syncthreads();  // the list is free again
     }
     if (clk) clk[15] = clock64() - clk[1];
-    // the sample has been read by every thread: start the stream proper (tile 0 is fetched again with the rest)
-    g0 = kStages;
-    if (tid == 0)
-      for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
   }
 
   // keep the M best of the list and raise the threshold to the weakest of them; all threads call it

@@ -1,0 +1,155 @@
+// The whole-row sampler kernel: rows whose candidate budget (top_k + history window) is too large for the
+// streaming kernel, in particular top_k = 0, where the reference orders and filters the WHOLE vocabulary
+// (qpack src/sampler.cpp:14,40-56; 12-26 ms per row on a CPU core).
+//
+// One cluster of 8 CTAs holds the row: every CTA copies its slice from HBM once (cp.async.bulk, no multicast)
+// and keeps it in shared memory as order-preserving 32-bit keys (plus the softmax numerators when they fit), so
+// that all later passes read shared memory only.  Nothing is sorted.  Each step of the reference chain becomes
+// a cluster-wide radix descent over the key bits, with per-CTA histograms summed over distributed shared memory:
+//   exact top-M / top-K cuts          count histograms, ties at the cut resolved by index (sampler.cpp:12-27,43-44)
+//   softmax numerators and sums       the C library's expf bit for bit, double sums in a fixed tree order (46-47)
+//   top-p cut and the drawn token     descents over histograms of probability MASS in 2^-62 fixed point, which
+//                                     find the first position of the value-ordered row whose running sum reaches
+//                                     top_p resp. the uniform draw (48-53, 58-63)
+// The fixed-point / tree sums differ from the reference's sequential double sums by about 1e-13 relative, so a
+// cut or a draw can land on the neighbouring element only when it lies that close to a boundary.
+#pragma once
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+#include "sample_stream.cuh"
+
+namespace qpb {
+
+constexpr int kWThreads = 512;
+constexpr int kWMaxCluster = 8;
+constexpr uint32_t kExcl = 0u;  // key of a column that has been cut
+
+struct WholeArgs {
+  StreamArgs s;      // same inputs / outputs as the streaming kernel (cand_io, n_shards unused)
+  int slice_cap;     // columns a CTA can hold
+  int have_e;        // 1: a float per column for the softmax numerator fits next to the keys
+};
+
+struct __align__(16) WholeSmem {
+  uint32_t hist[256];                // this CTA's count histogram (read by the whole cluster)
+  unsigned long long whist[256];     // this CTA's mass histogram
+  uint32_t thist[256];               // cluster totals, computed redundantly by every CTA
+  unsigned long long twhist[256];
+  unsigned long long xch[2][4];      // scalar exchange slots (read by the whole cluster), double-buffered
+  unsigned long long exp_tab[32];
+  uint64_t bar;
+  uint32_t sel[8];
+  unsigned long long sel64[4];
+  int warp_tot[kWThreads / 32];
+  double warp_sum[kWThreads / 32];
+  int pen_unique;
+  int out_count;
+  // followed by: penalty table (pen_slots ints), keys[slice_cap] (uint32), e[slice_cap] (float, optional)
+};
+
+struct WholeCtx {
+  WholeSmem *S;
+  uint32_t *keys;
+  float *ev;
+  int n;        // columns of this CTA
+  int per_t;    // columns per thread (odd, so that lanes fall on distinct banks)
+  int csize, crank;
+  int xslot;    // alternates between the two exchange buffers
+};
+
+// ---- cluster-wide helpers (every thread of every CTA of the cluster calls them) ---------------------------------
+
+// Sum of one unsigned value per CTA; also returns the sum over the CTAs of lower rank.
+__device__ __forceinline__ unsigned long long cluster_sum_u64(WholeCtx &c, unsigned long long mine,
+                                                             unsigned long long *below = nullptr) {
+  const int slot = c.xslot;
+  c.xslot ^= 1;
+  if (threadIdx.x == 0) c.S->xch[slot][0] = mine;
+  cooperative_groups::this_cluster().sync();
+  unsigned long long tot = 0, lo = 0;
+  for (int r = 0; r < c.csize; ++r) {
+    const unsigned long long v = cooperative_groups::this_cluster().map_shared_rank(c.S, r)->xch[slot][0];
+    tot += v;
+    if (r < c.crank) lo += v;
+  }
+  if (below) *below = lo;
+  return tot;  // the slot is rewritten two exchanges later at the earliest, with a cluster barrier in between
+}
+__device__ __forceinline__ double cluster_sum_f64(WholeCtx &c, double mine) {  // fixed order: rank 0, 1, ...
+  const int slot = c.xslot;
+  c.xslot ^= 1;
+  if (threadIdx.x == 0) c.S->xch[slot][1] = (unsigned long long)__double_as_longlong(mine);
+  cooperative_groups::this_cluster().sync();
+  double tot = 0.0;
+  for (int r = 0; r < c.csize; ++r)
+    tot += __longlong_as_double((long long)cooperative_groups::this_cluster().map_shared_rank(c.S, r)->xch[slot][1]);
+  return tot;
+}
+__device__ __forceinline__ uint32_t cluster_max_u32(WholeCtx &c, uint32_t mine) {
+  const int slot = c.xslot;
+  c.xslot ^= 1;
+  if (threadIdx.x == 0) c.S->xch[slot][2] = mine;
+  cooperative_groups::this_cluster().sync();
+  uint32_t m = 0;
+  for (int r = 0; r < c.csize; ++r) m = max(m, (uint32_t)cooperative_groups::this_cluster().map_shared_rank(c.S, r)->xch[slot][2]);
+  return m;
+}
+
+// block-wide helpers
+__device__ __forceinline__ int block_sum_int(WholeCtx &c, int v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) c.S->warp_tot[warp] = v;
+  __syncthreads();
+  int t = 0;
+  for (int w = 0; w < kWThreads / 32; ++w) t += c.S->warp_tot[w];
+  return t;
+}
+// exclusive prefix over the threads in order; total through *total
+__device__ __forceinline__ int block_excl_scan_int(WholeCtx &c, int v, int *total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();
+  if (lane == 31) c.S->warp_tot[warp] = incl;
+  __syncthreads();
+  int base = 0, tot = 0;
+  for (int w = 0; w < kWThreads / 32; ++w) {
+    const int t = c.S->warp_tot[w];
+    if (w < warp) base += t;
+    tot += t;
+  }
+  *total = tot;
+  return base + incl - v;
+}
+__device__ __forceinline__ double block_sum_f64(WholeCtx &c, double v) {  // fixed tree: lanes, then warps in order
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) c.S->warp_sum[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+  for (int w = 0; w < kWThreads / 32; ++w) t += c.S->warp_sum[w];
+  return t;
+}
+__device__ __forceinline__ uint32_t block_max_u32(WholeCtx &c, uint32_t v) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) c.S->warp_tot[warp] = (int)v;
+  __syncthreads();
+  uint32_t t = 0;
+  for (int w = 0; w < kWThreads / 32; ++w) t = max(t, (uint32_t)c.S->warp_tot[w]);
+  return t;
+}
+
+}  // namespace qpb

@@ -1,0 +1,232 @@
+// The whole-row kernel proper (see sample_whole.cuh for the design).
+#pragma once
+#include "sample_whole_passes.cuh"
+
+namespace qpb {
+namespace cg = cooperative_groups;
+
+__global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_constant__ WholeArgs wa) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const StreamArgs &a = wa.s;
+  WholeSmem &S = *reinterpret_cast<WholeSmem *>(smem_raw);
+  int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(WholeSmem));
+  uint32_t *keys = reinterpret_cast<uint32_t *>(pen_tab + a.pen_slots);
+  float *ev = wa.have_e ? reinterpret_cast<float *>(keys + wa.slice_cap) : nullptr;
+
+  WholeCtx c;
+  c.S = &S;
+  c.keys = keys;
+  c.ev = ev;
+  c.csize = (int)cg::this_cluster().num_blocks();
+  c.crank = (int)cg::this_cluster().block_rank();
+  c.xslot = 0;
+  const int tid = threadIdx.x;
+  const int row = a.row_list[blockIdx.x / c.csize];
+  const RowParams p = a.params[a.params_per_row ? row : 0];
+  long long hn = (a.history == nullptr) ? 0 : (a.hist_len ? a.hist_len[row] : a.hist_len_all);
+  const int V = a.vocab;  // whole rows are never vocabulary-sharded: vocab == vocab_total, id_offset == 0
+
+  // slice of this CTA, cut at multiples of 4 columns
+  int per = (V + c.csize - 1) / c.csize;
+  per = (per + 3) & ~3;
+  const int s0 = min(V, c.crank * per), s1 = min(V, s0 + per);
+  c.n = s1 - s0;
+  c.per_t = ((c.n + kWThreads - 1) / kWThreads) | 1;
+  const float *src = a.logits + (size_t)row * a.row_stride + s0;
+
+  if (tid == 0) {
+    mbar_init(&S.bar, 1);
+    mbar_fence_init();
+  }
+  if (tid < 32) S.exp_tab[tid] = kExp2Tab[tid];
+  __syncthreads();
+  // ---- the slice, HBM -> shared memory, once ----
+  const bool bulk = ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) && ((c.n & 3) == 0) && c.n > 0;
+  if (bulk && tid == 0) {
+    mbar_expect_tx(&S.bar, (uint32_t)c.n * 4u);
+    for (int off = 0; off < c.n; off += 4096)  // 16 KB per copy
+      bulk_g2s(keys + off, src + off, (uint32_t)min(4096, c.n - off) * 4u, &S.bar);
+  }
+  MtFetch rng = {};
+  const bool leader0 = c.crank == 0 && tid == 0;
+  if (leader0 && a.draw) rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+
+  // penalty set (sampler.cpp:32-38), while the copies are in flight
+  const bool use_pen = p.repeat_penalty != 1.f && a.history != nullptr;
+  hn = hn < 0 ? 0 : (hn > a.hist_stride ? a.hist_stride : hn);
+  long long hfrom = 0;
+  if (p.repeat_last_n >= 0 && hn > (long long)p.repeat_last_n) hfrom = hn - p.repeat_last_n;
+  const int *hrow = a.history + (size_t)row * a.hist_stride;
+  int npen = 0;
+  if (use_pen) {
+    for (int i = tid; i < a.pen_slots; i += kWThreads) pen_tab[i] = kPenEmpty;
+    if (tid == 0) S.pen_unique = 0;
+    __syncthreads();
+    int mine = 0;
+    for (long long i = hfrom + tid; i < hn; i += kWThreads) mine += pen_insert(pen_tab, a.pen_slots, hrow[i], V, a.status);
+    if (mine) atomicAdd(&S.pen_unique, mine);
+    __syncthreads();
+    npen = S.pen_unique;
+  }
+  const bool greedy = p.temperature <= 0.f;
+  const long long K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, V) : V);  // sampler.cpp:39-40
+  long long M = min((long long)V, K + npen);
+  if (M >= V / 4) M = V;  // top_m returns the whole row in this case (sampler.cpp:14)
+
+  bool failed = false;
+  if (bulk) {
+    if (!mbar_wait_bounded(&S.bar, 0u)) failed = true;
+  } else {
+    for (int i = tid; i < c.n; i += kWThreads) keys[i] = __float_as_uint(src[i]);
+    __syncthreads();
+  }
+  if (failed && tid == 0) atomicOr(a.status, ST_COPY_TIMEOUT);
+  // floats -> order-preserving keys, in place; each thread owns the columns [tid * per_t, (tid + 1) * per_t)
+  const int i0 = tid * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  for (int i = i0; i < i1; ++i) keys[i] = f2key(__uint_as_float(keys[i]));
+  __syncthreads();
+
+  // ---- the M best raw columns (sampler.cpp:12-27), penalty on them (42), the K best after it (43-44) ----
+  unsigned long long in_count = (unsigned long long)V;
+  if (M < in_count) { cluster_keep_top(c, (unsigned long long)M); in_count = (unsigned long long)M; }
+  if (npen > 0) {
+    const float rp = p.repeat_penalty;
+    for (int sidx = tid; sidx < a.pen_slots; sidx += kWThreads) {
+      const int id = pen_tab[sidx];
+      if (id >= s0 && id < s1) {
+        const uint32_t k = keys[id - s0];
+        if (k != kExcl) {
+          float v = key2f(k);
+          v = v > 0.f ? __fdiv_rn(v, rp) : __fmul_rn(v, rp);
+          keys[id - s0] = f2key(v);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if ((unsigned long long)K < in_count) { cluster_keep_top(c, (unsigned long long)K); in_count = (unsigned long long)K; }
+
+  // ---- top value ----
+  uint32_t kmax = 0;
+  for (int i = i0; i < i1; ++i) kmax = max(kmax, keys[i]);
+  kmax = cluster_max_u32(c, block_max_u32(c, kmax));
+  const float mx = key2f(kmax);
+
+  unsigned long long keep = in_count;
+  int picked = -1;
+  double tot = 1.0;
+  if (greedy) {  // sampler.cpp:45: the best column, probability 1, no random word
+    keep = 1;
+    picked = cluster_id_of_jth(c, kmax, 1ULL, s0);
+  } else {
+    // ---- softmax numerators (sampler.cpp:46-47) and their sum ----
+    const float T = p.temperature;
+    auto e_of = [&](int i, uint32_t k) -> float {
+      return ev ? ev[i] : expf_libm(__fdiv_rn(__fsub_rn(key2f(k), mx), T), S.exp_tab);
+    };
+    double part = 0.0;
+    for (int i = i0; i < i1; ++i) {
+      const uint32_t k = keys[i];
+      if (k != kExcl) {
+        const float e = expf_libm(__fdiv_rn(__fsub_rn(key2f(k), mx), T), S.exp_tab);
+        if (ev) ev[i] = e;
+        part += (double)e;
+      }
+    }
+    const double sum = cluster_sum_f64(c, block_sum_f64(c, part));
+    // ---- min-p (sampler.cpp:50): numerators fall along the order, so the columns that pass form a prefix ----
+    const float e0 = expf_libm(__fdiv_rn(__fsub_rn(mx, mx), T), S.exp_tab);
+    unsigned long long keep_a = in_count;
+    if (p.min_p > 0.f) {
+      const float thr = __fmul_rn(p.min_p, e0);
+      int pass = 0;
+      for (int i = i0; i < i1; ++i) {
+        const uint32_t k = keys[i];
+        if (k != kExcl && !(e_of(i, k) < thr)) ++pass;
+      }
+      keep_a = cluster_sum_u64(c, (unsigned long long)block_sum_int(c, pass));
+      if (keep_a < 1ULL) keep_a = 1ULL;
+    }
+    // ---- top-p (sampler.cpp:51): first position whose running sum of e / sum reaches top_p ----
+    unsigned long long keep_b = in_count;
+    if (p.top_p < 1.f) {
+      const double tp = (double)p.top_p;
+      const unsigned long long target = tp <= 0.0 ? 1ULL : __double2ull_ru(tp * 0x1p62);
+      const MassPos mp = cluster_mass_find(c, target, [&](int i, uint32_t k) -> unsigned long long {
+        return __double2ull_rz(__ddiv_rn((double)e_of(i, k), sum) * 0x1p62);
+      });
+      if (mp.found) keep_b = mp.pos;
+    }
+    keep = keep_a < keep_b ? keep_a : keep_b;
+    if (keep < in_count) cluster_keep_top(c, keep);
+    // ---- renormalise (sampler.cpp:54-55) ----
+    part = 0.0;
+    for (int i = i0; i < i1; ++i) {
+      const uint32_t k = keys[i];
+      if (k != kExcl) part += (double)e_of(i, k);
+    }
+    tot = cluster_sum_f64(c, block_sum_f64(c, part));
+    // ---- draw (sampler.cpp:58-63) ----
+    if (a.draw) {
+      if (keep == 1ULL) {
+        picked = cluster_id_of_jth(c, kmax, 1ULL, s0);
+      } else {
+        unsigned long long w = 0;
+        if (leader0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+        // the word travels from the leader to everybody through an exchange slot
+        w = cluster_sum_u64(c, leader0 ? w : 0ULL);
+        const double u = word_to_uniform(w);
+        const unsigned long long target = __double2ull_ru(u * 0x1p62);
+        const MassPos mp = cluster_mass_find(c, target, [&](int i, uint32_t k) -> unsigned long long {
+          const float pr = __double2float_rn(__ddiv_rn((double)e_of(i, k), tot));
+          return __double2ull_rz((double)pr * 0x1p62);
+        });
+        if (mp.found) {
+          picked = cluster_id_of_jth(c, mp.key, mp.j, s0);
+        } else {  // rounding left the total below u: the reference returns the last pair (sampler.cpp:62)
+          uint32_t inv = 0;
+          for (int i = i0; i < i1; ++i)
+            if (keys[i] != kExcl) inv = max(inv, ~keys[i]);
+          const uint32_t kmin = ~cluster_max_u32(c, block_max_u32(c, inv));
+          int cnt = 0;
+          for (int i = i0; i < i1; ++i) cnt += keys[i] == kmin;
+          const unsigned long long e_cnt = cluster_sum_u64(c, (unsigned long long)block_sum_int(c, cnt));
+          picked = cluster_id_of_jth(c, kmin, e_cnt, s0);
+        }
+      }
+    }
+  }
+
+  // ---- outputs ----
+  if (leader0) {
+    if (a.draw && a.out_ids) a.out_ids[row] = picked;
+    if (a.dist_count) a.dist_count[row] = (int)keep;
+  }
+  if (a.dist_ids && a.max_out > 0) {  // the kept pairs, in no particular order
+    int mine = 0;
+    for (int i = i0; i < i1; ++i) mine += keys[i] != kExcl;
+    int total = 0;
+    const int base = block_excl_scan_int(c, mine, &total);
+    unsigned long long below = 0;
+    cluster_sum_u64(c, (unsigned long long)total, &below);
+    long long pos = (long long)below + base;
+    const float T = p.temperature;
+    for (int i = i0; i < i1; ++i) {
+      const uint32_t k = keys[i];
+      if (k == kExcl) continue;
+      if (pos < a.max_out) {
+        float pr = 1.f;
+        if (!greedy) {
+          const float e = ev ? ev[i] : expf_libm(__fdiv_rn(__fsub_rn(key2f(k), mx), T), S.exp_tab);
+          pr = __double2float_rn(__ddiv_rn((double)e, tot));
+        }
+        a.dist_ids[(size_t)row * a.max_out + pos] = s0 + i;
+        a.dist_p[(size_t)row * a.max_out + pos] = pr;
+      }
+      ++pos;
+    }
+  }
+  cooperative_groups::this_cluster().sync();  // nobody leaves while its shared memory may still be read
+}
+
+}  // namespace qpb

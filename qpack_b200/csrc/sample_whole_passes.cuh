@@ -1,0 +1,218 @@
+// Cluster-wide radix passes of the whole-row kernel: count descent (exact top-N cut with index tie-break),
+// mass descent (first position of the value-ordered row whose running mass reaches a target) and the lookup of
+// the j-th column of a given key in index order.
+#pragma once
+#include "sample_whole.cuh"
+
+namespace qpb {
+
+// One histogram pass over the 8-bit digit at `shift` of every column that is still in and matches
+// (key & mask) == prefix.  Leaves the cluster totals in S->thist (and S->twhist when WEIGHTED) of every CTA.
+template <bool WEIGHTED, class WeightFn>
+__device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, uint32_t mask, int shift, WeightFn wf) {
+  WholeSmem *S = c.S;
+  if (threadIdx.x < 256) {
+    S->hist[threadIdx.x] = 0;
+    if (WEIGHTED) S->whist[threadIdx.x] = 0ULL;
+  }
+  __syncthreads();
+  const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  for (int i = i0; i < i1; ++i) {
+    const uint32_t k = c.keys[i];
+    if (k != kExcl && (k & mask) == prefix) {
+      const uint32_t d = (k >> shift) & 255u;
+      atomicAdd(&S->hist[d], 1u);
+      if (WEIGHTED) atomicAdd(&S->whist[d], wf(i, k));
+    }
+  }
+  cooperative_groups::this_cluster().sync();  // every CTA's histogram is complete
+  if (threadIdx.x < 256) {
+    uint32_t t = 0;
+    unsigned long long tw = 0;
+    for (int r = 0; r < c.csize; ++r) {
+      const WholeSmem *R = cooperative_groups::this_cluster().map_shared_rank(S, r);
+      t += R->hist[threadIdx.x];
+      if (WEIGHTED) tw += R->whist[threadIdx.x];
+    }
+    S->thist[threadIdx.x] = t;
+    if (WEIGHTED) S->twhist[threadIdx.x] = tw;
+  }
+  cooperative_groups::this_cluster().sync();  // every CTA has read every histogram: they may be cleared again
+}
+
+struct NoWeight {
+  __device__ unsigned long long operator()(int, uint32_t) const { return 0ULL; }
+};
+
+// Exclusive rank, in index order over the whole cluster, of this thread's first column with key == kk.
+__device__ __forceinline__ long long ordered_rank_of_equal(WholeCtx &c, uint32_t kk) {
+  const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  int mine = 0;
+  for (int i = i0; i < i1; ++i) mine += c.keys[i] == kk;
+  int total = 0;
+  const int base = block_excl_scan_int(c, mine, &total);
+  unsigned long long below = 0;
+  cluster_sum_u64(c, (unsigned long long)total, &below);
+  return (long long)below + base;
+}
+
+// Keeps the `want` best columns that are still in, by (key descending, index ascending), and cuts the others
+// (sampler.cpp:12-27 for the M raw candidates, 43-44 for the K best after the penalty).  1 <= want < columns in.
+__device__ void cluster_keep_top(WholeCtx &c, unsigned long long want) {
+  WholeSmem *S = c.S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t prefix = 0, mask = 0;
+  unsigned long long need = want;
+  bool whole_bucket = false;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    cluster_hist_pass<false>(c, prefix, mask, shift, NoWeight());
+    if (warp == 0) {
+      uint32_t loc[8];
+      unsigned long long s = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { loc[k] = S->thist[8 * lane + k]; s += loc[k]; }
+      unsigned long long suf = s;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += t;
+      }
+      const unsigned long long above = suf - s;
+      if (above < need && need <= suf) {
+        unsigned long long acc = above;
+#pragma unroll
+        for (int k = 7; k >= 0; --k) {
+          if (acc + loc[k] >= need) { S->sel[0] = 8 * lane + k; S->sel64[0] = need - acc; S->sel[1] = loc[k]; break; }
+          acc += loc[k];
+        }
+      }
+    }
+    __syncthreads();
+    const uint32_t d = S->sel[0], bucket = S->sel[1];
+    need = S->sel64[0];
+    prefix |= d << shift;
+    mask |= 0xffu << shift;
+    __syncthreads();
+    if (need == bucket) { whole_bucket = true; break; }
+  }
+  const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  if (whole_bucket) {  // every column of the chosen bucket stays: cut what lies below it
+    for (int i = i0; i < i1; ++i)
+      if ((c.keys[i] & mask) < prefix) c.keys[i] = kExcl;
+  } else {  // prefix is the exact key at the cut; `need` of its columns stay, the lowest indices first
+    const long long rank0 = ordered_rank_of_equal(c, prefix);
+    long long rank = rank0;
+    for (int i = i0; i < i1; ++i) {
+      const uint32_t k = c.keys[i];
+      if (k < prefix) c.keys[i] = kExcl;
+      else if (k == prefix) { if ((unsigned long long)rank >= need) c.keys[i] = kExcl; ++rank; }
+    }
+  }
+  __syncthreads();
+}
+
+struct MassPos {
+  bool found;               // false: the total mass stays below the target
+  uint32_t key;             // key of the column where the running mass reaches the target
+  unsigned long long pos;   // 1-based position of that column in the value-ordered row
+  unsigned long long j;     // 1-based rank of that column among the columns of the same key, in index order
+};
+
+// First position of the row ordered by (key descending, index ascending) whose running mass reaches `target`
+// (sampler.cpp:49-52 with mass = e / sum and target = top_p; sampler.cpp:60-61 with mass = p and target = u).
+// Masses are 2^-62 fixed point so that the histogram sums do not depend on the order of the additions.
+template <class WeightFn>
+__device__ MassPos cluster_mass_find(WholeCtx &c, unsigned long long target, WeightFn wf) {
+  WholeSmem *S = c.S;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (target == 0ULL) target = 1ULL;
+  uint32_t prefix = 0, mask = 0;
+  unsigned long long w_above = 0, g_above = 0, bucket_w = 0, bucket_n = 0;
+  MassPos out = {false, 0u, 0ULL, 0ULL};
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    cluster_hist_pass<true>(c, prefix, mask, shift, wf);
+    if (threadIdx.x == 0) S->sel[2] = 0u;
+    __syncthreads();
+    if (warp == 0) {
+      unsigned long long locw[8], sw = 0, sn = 0;
+      uint32_t locn[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        locw[k] = S->twhist[8 * lane + k];
+        locn[k] = S->thist[8 * lane + k];
+        sw += locw[k];
+        sn += locn[k];
+      }
+      unsigned long long sufw = sw, sufn = sn;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long tw = __shfl_down_sync(0xffffffffu, sufw, o);
+        const unsigned long long tn = __shfl_down_sync(0xffffffffu, sufn, o);
+        if (lane + o < 32) { sufw += tw; sufn += tn; }
+      }
+      const unsigned long long abovew = w_above + sufw - sw, aboven = sufn - sn;
+      if (abovew < target && target <= abovew + sw) {  // the crossing lies in this lane's eight bins
+        unsigned long long accw = abovew, accn = aboven;
+#pragma unroll
+        for (int k = 7; k >= 0; --k) {
+          if (accw + locw[k] >= target) {
+            S->sel[2] = 1u;
+            S->sel[3] = 8 * lane + k;
+            S->sel64[0] = accw;          // mass strictly above the chosen bucket
+            S->sel64[1] = accn;          // columns strictly above it within this pass
+            S->sel64[2] = locw[k];
+            S->sel64[3] = locn[k];
+            break;
+          }
+          accw += locw[k];
+          accn += locn[k];
+        }
+      }
+    }
+    __syncthreads();
+    const bool hit = S->sel[2] != 0u;
+    const uint32_t d = S->sel[3];
+    if (hit) {
+      w_above = S->sel64[0];
+      g_above += S->sel64[1];
+      bucket_w = S->sel64[2];
+      bucket_n = S->sel64[3];
+    }
+    __syncthreads();
+    if (!hit) return out;
+    prefix |= d << shift;
+    mask |= 0xffu << shift;
+  }
+  // all bucket_n columns of key `prefix` carry the same mass
+  const unsigned long long each = bucket_n ? bucket_w / bucket_n : 0ULL;
+  unsigned long long j = 1;
+  if (each > 0ULL) j = (target - w_above + each - 1ULL) / each;
+  j = j < 1ULL ? 1ULL : (j > bucket_n ? bucket_n : j);
+  out.found = true;
+  out.key = prefix;
+  out.pos = g_above + j;
+  out.j = j;
+  return out;
+}
+
+// Global id of the j-th (1-based) column with key kk in index order; the same value in every thread of the cluster.
+__device__ int cluster_id_of_jth(WholeCtx &c, uint32_t kk, unsigned long long j, int first_global_id) {
+  const long long rank0 = ordered_rank_of_equal(c, kk);
+  const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  const int slot = c.xslot;
+  c.xslot ^= 1;
+  if (threadIdx.x == 0) c.S->xch[slot][3] = 0ULL;
+  __syncthreads();
+  long long rank = rank0;
+  for (int i = i0; i < i1; ++i)
+    if (c.keys[i] == kk) {
+      if ((unsigned long long)rank + 1ULL == j) c.S->xch[slot][3] = (unsigned long long)(first_global_id + i) + 1ULL;
+      ++rank;
+    }
+  cooperative_groups::this_cluster().sync();
+  unsigned long long v = 0;
+  for (int r = 0; r < c.csize; ++r) v = max(v, cooperative_groups::this_cluster().map_shared_rank(c.S, r)->xch[slot][3]);
+  return (int)v - 1;
+}
+
+}  // namespace qpb

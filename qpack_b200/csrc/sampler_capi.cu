@@ -11,6 +11,7 @@
 
 #include "../../include/qpack_b200_sampler.h"
 #include "sample_stream.cuh"
+#include "sample_whole_kernel.cuh"
 
 using namespace qpb;
 
@@ -32,6 +33,7 @@ struct qpb_sampler {
   int routed_rows = -1, routed_vocab = -1, n_stream = 0, n_whole = 0, max_window = 0;
   long long routed_hist_cap = -1;
   int cluster = 0;
+  int stream_slots = 0;  // CTAs of the streaming kernel resident on the GPU at once (0: not queried yet)
   bool attr_done[4] = {false, false, false, false};
   int64_t launches = 0;
   // staging for the host-buffer entry point
@@ -131,6 +133,11 @@ int launch_stream(qpb_sampler *s, const StreamArgs &args, int rows, int cluster,
   if (!s->attr_done[MODE]) {  // once per handle (the attribute is per device)
     QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     s->attr_done[MODE] = true;
+    if (MODE == MODE_SAMPLE) {
+      int per_sm = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stream_rows_kernel<MODE>, kThreads, smem) == cudaSuccess && per_sm > 0)
+        s->stream_slots = per_sm * s->sm_count;
+    }
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(rows * cluster), 1, 1);
@@ -194,9 +201,49 @@ void fill_common(qpb_sampler *s, const Inputs &in, StreamArgs &a) {
   a.phase_clk = s->d_phase_clk;
 }
 
-// rows whose candidate budget exceeds the streaming kernel's take the whole-row kernel
-int launch_whole(qpb_sampler *s, const Inputs &, int32_t *, float *, int32_t *, int, int32_t *, bool, cudaStream_t) {
-  return fail(s, QPB_ERR_UNSUPPORTED, "rows with top_k + window > 768 are not supported yet");
+// Rows whose candidate budget exceeds the streaming kernel's take the whole-row kernel: one cluster per row,
+// the row resident in the cluster's shared memory.
+int launch_whole(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dist_p, int32_t *d_dist_count,
+                 int max_out, int32_t *d_out_ids, bool draw, cudaStream_t st) {
+  const int cluster = in.vocab >= 8192 ? kWMaxCluster : 1;
+  int per = (in.vocab + cluster - 1) / cluster;
+  per = (per + 3) & ~3;
+  WholeArgs wa = {};
+  fill_common(s, in, wa.s);
+  wa.s.n_rows = s->n_whole;
+  wa.s.row_list = s->d_rows_whole;
+  wa.s.out_ids = d_out_ids;
+  wa.s.draw = draw ? 1 : 0;
+  wa.s.dist_ids = d_dist_ids;
+  wa.s.dist_p = d_dist_p;
+  wa.s.dist_count = d_dist_count;
+  wa.s.max_out = max_out;
+  wa.slice_cap = per;
+  const size_t fixed = sizeof(WholeSmem) + (size_t)wa.s.pen_slots * sizeof(int);
+  const size_t limit = 227 * 1024;
+  if (fixed + (size_t)per * 4 > limit)
+    return fail(s, QPB_ERR_UNSUPPORTED, "vocabulary too large for the whole-row kernel (about 440k columns)");
+  wa.have_e = fixed + (size_t)per * 8 <= limit ? 1 : 0;
+  const size_t smem = fixed + (size_t)per * (wa.have_e ? 8 : 4);
+  if (!s->attr_done[3]) {
+    QPB_CUDA(s, cudaFuncSetAttribute(whole_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+    s->attr_done[3] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(s->n_whole * cluster), 1, 1);
+  cfg.blockDim = dim3(kWThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = (unsigned)cluster;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  QPB_CUDA(s, cudaLaunchKernelEx(&cfg, whole_rows_kernel, wa));
+  s->launches++;
+  return QPB_OK;
 }
 void whole_free(qpb_sampler *) {}
 
@@ -211,15 +258,33 @@ int run_rows(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dis
   if (s->n_stream > 0) {
     StreamArgs a = {};
     fill_common(s, in, a);
-    a.n_rows = s->n_stream;
-    a.row_list = (s->n_stream == in.n_rows) ? nullptr : s->d_rows_stream;
     a.out_ids = d_out_ids;
     a.draw = draw ? 1 : 0;
     a.dist_ids = d_dist_ids;
     a.dist_p = d_dist_p;
     a.dist_count = d_dist_count;
     a.max_out = max_out;
-    rc = launch_stream<MODE_SAMPLE>(s, a, s->n_stream, pick_cluster(s, s->n_stream), st);
+    // One CTA per row fills the GPU in waves of `slots` rows.  A last wave that would be less than half full is
+    // launched first, with its rows split over clusters of up to 8 CTAs so that it, too, covers every SM.
+    const int n = s->n_stream;
+    const int slots = s->stream_slots > 0 ? s->stream_slots : 3 * s->sm_count;
+    int head = 0, head_cluster = 1;
+    if (!s->cluster && n > slots) {
+      const int rem = n % slots;
+      if (rem > 0 && 2 * rem <= slots) {
+        head = rem;
+        head_cluster = slots / rem > 8 ? 8 : slots / rem;
+      }
+    }
+    if (head > 0) {
+      a.n_rows = head;
+      a.row_list = s->d_rows_stream;
+      rc = launch_stream<MODE_SAMPLE>(s, a, head, head_cluster, st);
+      if (rc) return rc;
+    }
+    a.n_rows = n - head;
+    a.row_list = s->d_rows_stream + head;
+    rc = launch_stream<MODE_SAMPLE>(s, a, n - head, head ? 1 : pick_cluster(s, n), st);
     if (rc) return rc;
   }
   if (s->n_whole > 0) {
@@ -414,8 +479,7 @@ int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state313) {
 
 int qpb_sampler_set_cluster(qpb_sampler *s, int cluster) {
   if (!s) return QPB_ERR_INVALID;
-  if (cluster != 0 && cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8)
-    return fail(s, QPB_ERR_INVALID, "cluster must be 0, 1, 2, 4 or 8");
+  if (cluster < 0 || cluster > 8) return fail(s, QPB_ERR_INVALID, "cluster must be 0 (automatic) or 1..8");
   s->cluster = cluster;
   return QPB_OK;
 }

@@ -1,0 +1,90 @@
+"""GPU parity tests of the whole-row kernel (rows with top_k off or a candidate budget above the streaming
+kernel's), through the C ABI, against the CPU checker.  Ids are bit-exact unless the draw lies within 1e-6 of a
+CDF boundary (counted); survivor counts equal; probabilities within 1e-5 (the kernel sums in a fixed tree order
+where the reference sums sequentially, so last-bit differences are expected and counted)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import Oracle, make_params
+from qpack_b200 import synth
+from qpack_b200.sampler import BatchSampler
+
+from helpers import compare_rows
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def device_rows(wl, max_out):
+    B = wl.rows
+    bs = BatchSampler(B, 0)
+    bs.set_params(wl.params)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    d_h = torch.from_numpy(wl.history).to(DEV) if wl.history is not None else None
+    d_hl = torch.from_numpy(wl.hist_len).to(DEV) if wl.hist_len is not None else None
+    ids, p, cnt, out = bs.dist(d_x, d_h, d_hl, max_out=max_out, draw=True)
+    bs.check()
+    res = (out.cpu().numpy(), cnt.cpu().numpy(), ids.cpu().numpy(), p.cpu().numpy())
+    bs.close()
+    return res
+
+
+def first_uniforms(params):
+    return [Oracle(params[r:r + 1]).next_uniform() for r in range(len(params))]
+
+
+def test_llama3_vocab_batch_top_k_off():
+    """Config 2: V = 128256, temperature 1, top_p 0.9, top_k off: flat rows keep ~78k tokens, peaked rows a few."""
+    wl = synth.llama3_batch(rows=16)
+    V = wl.vocab
+    exp = Oracle.sample_rows(wl.params, wl.logits, None, None, max_out=V)
+    got = device_rows(wl, V)
+    rep = compare_rows(*got, exp, uniforms=first_uniforms(wl.params), ordered=False)
+    assert rep["id_mismatch"] == rep["near_boundary"]
+    assert int(exp["count"].max()) > 50000 and int(exp["count"].min()) < 10000
+    print("llama3 batch report:", rep)
+
+
+def test_mixed_parameter_batch():
+    """Config 3: V = 201088, heterogeneous rows: greedy, top_k in {0, 20, 50, 200}, penalties over 128 ids.  The
+    batch is split between the two kernels; every row must agree with the checker."""
+    wl = synth.mixed_batch(rows=48)
+    V = wl.vocab
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=V)
+    got = device_rows(wl, V)
+    rep = compare_rows(*got, exp, uniforms=first_uniforms(wl.params), ordered=False)
+    assert rep["id_mismatch"] == rep["near_boundary"]
+    assert (wl.params["top_k"] == 0).any() and (wl.params["temperature"] == 0).any()
+    print("mixed batch report:", rep)
+
+
+def test_large_top_k_with_penalty_and_ties():
+    """A top_k far above the streaming kernel's budget, a penalty below and above 1, heavy ties at the cuts."""
+    rng = np.random.default_rng(5)
+    V = 50000
+    x = np.round(rng.standard_normal((6, V)) * 3).astype(np.float32)  # ~20 distinct values: every cut splits ties
+    hist = rng.integers(0, V, size=(6, 300)).astype(np.int32)
+    p = make_params(6, temperature=[0.7, 1.0, 1.3, 0.0, 0.9, 1.1], top_k=[5000, 0, 20000, 3000, 900, 0],
+                    top_p=[0.9, 0.95, 1.0, 0.9, 0.5, 0.99], min_p=[0.0, 0.01, 0.0, 0.0, 0.05, 0.0],
+                    repeat_penalty=[1.2, 0.8, 1.0, 1.1, 1.3, 0.9], repeat_last_n=[300, 300, 64, -1, 128, 300],
+                    seed=np.arange(11, 17).astype(np.uint64))
+    wl = synth.Workload("ties", x, p, hist, np.full(6, 300, np.int32))
+    exp = Oracle.sample_rows(p, x, hist, wl.hist_len, max_out=V)
+    got = device_rows(wl, V)
+    rep = compare_rows(*got, exp, uniforms=first_uniforms(p), ordered=False)
+    assert rep["id_mismatch"] == rep["near_boundary"]
+
+
+def test_successive_draws_share_the_rng_stream():
+    wl = synth.llama3_batch(rows=4)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    bs = BatchSampler(4, 0)
+    bs.set_params(wl.params)
+    seqs = [bs.sample(d_x).cpu().numpy() for _ in range(4)]
+    bs.check()
+    bs.close()
+    for r in range(4):
+        o = Oracle(wl.params[r:r + 1])
+        want = [o.sample(wl.logits[r]) for _ in range(4)]
+        assert want == [int(s[r]) for s in seqs]
