@@ -80,7 +80,7 @@ QPB_API int qpb_sampler_sample_batch(qpb_sampler *s, const float *d_logits, int6
  * pairs, most likely first, into d_dist_ids / d_dist_p [n_rows][max_out] (first max_out pairs) with the full
  * pair count in d_dist_count[r].  If d_out_ids is not NULL the draw of qp::Sampler::draw (src/sampler.cpp:58-63)
  * is made as well, otherwise the RNG is left untouched.  Rows whose candidate budget top_k + window exceeds
- * 768 (top_k off, or very large) report their pairs in no particular order. */
+ * 500 (top_k off, or very large) report their pairs in no particular order. */
 QPB_API int qpb_sampler_dist_batch(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
                            const int32_t *d_history, int64_t hist_stride, const int32_t *d_hist_len, int hist_len_all,
                            int32_t *d_dist_ids, float *d_dist_p, int32_t *d_dist_count, int max_out,

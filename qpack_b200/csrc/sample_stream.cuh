@@ -24,19 +24,21 @@ namespace cg = cooperative_groups;
 
 constexpr int kThreads = 256;                // threads per CTA
 constexpr int kTile = 4096;                  // floats per ring stage (16 KB)
-constexpr int kStages = 3;                   // ring depth: 48 KB in flight per CTA
-constexpr int kHalf = kTile / 2;             // a tile is scanned as two halves of 8 floats per thread
-constexpr int kCandCap = 2816;               // candidate entries of the streaming phase (22 KB)
-constexpr int kCandHigh = kCandCap - kHalf;  // careful mode: select when the list grows beyond this (a half adds <= kHalf)
-constexpr int kCandHighFast = 1792;          // fast mode: select after a tile that left more than this
+constexpr int kStages = 2;                   // ring depth: 32 KB in flight per CTA, 4 CTAs per SM
+constexpr int kChunk = kThreads * 4;         // careful mode scans a tile in chunks of one float4 per thread
+constexpr int kCandCap = 2048;               // candidate entries of the streaming phase (16 KB)
+constexpr int kCandHigh = kCandCap - kChunk; // careful mode: select when the list grows beyond this (a chunk adds <= kChunk)
+constexpr int kCandHighFast = 1280;          // fast mode: select after a tile that left more than this
 constexpr int kRingEntries = kStages * kTile * 4 / 8;
 constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to the cluster merge (ring reused)
 // Rows with top_k + window above this take the whole-row kernel instead.  It also bounds the "whole row" case of
-// top_m (M >= V/4 implies V <= 4 * 700 + 3 = 2803 <= kCandCap).
-constexpr int kSmallMaxM = 700;
+// top_m (M >= V/4 implies V <= 4 * 500 + 3 = 2003 <= kCandCap).
+constexpr int kSmallMaxM = 500;
+constexpr int kPenBloomBits = 4096;          // one-probe negative test in front of the penalty hash table
 constexpr int kPenEmpty = -1;
 static_assert(kSmallMaxM <= kCandHigh && 4 * kSmallMaxM + 3 <= kCandCap, "candidate list sizing");
 static_assert(8 * kSmallMaxM <= kMergeCap, "cluster merge sizing");
+static_assert(kTile % kChunk == 0, "chunking");
 
 enum : int { MODE_SAMPLE = 0, MODE_LOCAL_TOPM = 1, MODE_MERGE = 2 };
 
@@ -77,6 +79,7 @@ struct __align__(16) StreamSmem {
   uint64_t full[kStages];
   unsigned long long exp_tab[32];
   uint32_t hist[256];
+  uint32_t pen_bloom[kPenBloomBits / 32];
   uint32_t sel[4];
   int cand_count;
   int pen_unique;
@@ -86,6 +89,9 @@ struct __align__(16) StreamSmem {
 
 // ---- penalty set: open-addressing hash set of the distinct in-range ids of the window (sampler.cpp:32-38) ------
 __device__ __forceinline__ uint32_t pen_hash(int id, int slots) { return ((uint32_t)id * 2654435761u) & (uint32_t)(slots - 1); }
+
+__device__ __forceinline__ uint32_t pen_bloom_bit(int id) { return ((uint32_t)id * 0x9E3779B1u) >> (32 - 12); }
+static_assert(kPenBloomBits == 1 << 12, "pen_bloom_bit takes 12 hash bits");
 
 __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) {
   uint32_t h = pen_hash(id, slots);
@@ -101,13 +107,16 @@ __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) 
 // Part 1 (no barrier): clears the table and fetches this thread's first id of the window, so that the global
 // load is in flight while other work goes on.  window = [from, hn) of hist.
 __device__ __forceinline__ int pen_prefetch(int *tab, int slots, int *unique_ctr, const int *hist, long long from,
-                                            long long hn) {
+                                            long long hn, uint32_t *bloom) {
   for (int i = threadIdx.x; i < slots; i += kThreads) tab[i] = kPenEmpty;
+  if (threadIdx.x < kPenBloomBits / 32) bloom[threadIdx.x] = 0u;
   if (threadIdx.x == 0) *unique_ctr = 0;
   return (from + threadIdx.x < hn) ? hist[from + threadIdx.x] : -1;
 }
-__device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_total, int *status) {
+__device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_total, int *status,
+                                          uint32_t *bloom = nullptr) {
   if (t < 0 || t >= vocab_total) return 0;  // out-of-range ids are skipped (sampler.cpp:36)
+  if (bloom) { const uint32_t b = pen_bloom_bit(t); atomicOr(&bloom[b >> 5], 1u << (b & 31)); }
   uint32_t h = pen_hash(t, slots);
   for (int probe = 0; probe < slots; ++probe) {
     const int old = atomicCAS(&tab[h], kPenEmpty, t);
@@ -120,10 +129,10 @@ __device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_
 }
 // Part 2 (a barrier must separate it from part 1): inserts the window, returns the number of distinct ids.
 __device__ int pen_build(int *tab, int slots, int *unique_ctr, const int *hist, long long from, long long hn,
-                         int first_id, int vocab_total, int *status) {
-  int mine = pen_insert(tab, slots, first_id, vocab_total, status);
+                         int first_id, int vocab_total, int *status, uint32_t *bloom) {
+  int mine = pen_insert(tab, slots, first_id, vocab_total, status, bloom);
   for (long long i = from + kThreads + threadIdx.x; i < hn; i += kThreads)
-    mine += pen_insert(tab, slots, hist[i], vocab_total, status);
+    mine += pen_insert(tab, slots, hist[i], vocab_total, status, bloom);
   if (mine) atomicAdd(unique_ctr, mine);
   __syncthreads();
   return *unique_ctr;
@@ -233,7 +242,8 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     for (int i = threadIdx.x; i < n; i += kThreads) {
       const unsigned long long c = cand[i];
       const int id = comp_id(c);
-      if (pen_contains(pen_tab, a.pen_slots, id)) {
+      const uint32_t b = pen_bloom_bit(id);
+      if (((S.pen_bloom[b >> 5] >> (b & 31)) & 1u) && pen_contains(pen_tab, a.pen_slots, id)) {
         float v = key2f(comp_key(c));
         v = v > 0.f ? __fdiv_rn(v, rp) : __fmul_rn(v, rp);
         cand[i] = make_comp(f2key(v), (uint32_t)id);
@@ -241,8 +251,10 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     }
     __syncthreads();
   }
+  if (clk) clk[11] = clock64();
   // the K best by (value desc, id asc) (sampler.cpp:43-44): select, then rank = number of larger composites
   n = block_keep_top(cand, n, K, S.hist, S.sel, &S.cand_count);
+  if (clk) clk[12] = clock64();
   const int nK = n;
   {
     // P lanes share one entry (P = 32, 16, 8, 4, 2 or 1, as many as the CTA can spare), each counting over a
@@ -339,7 +351,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
 
 // ---- the kernel ----------------------------------------------------------------------------------------------
 template <int MODE>
-__global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
   int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
@@ -357,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
   const bool want_rng = MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw;
   const int Vt = a.vocab_total;
   long long *clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
-  long long select_clk = 0, wait_clk = 0, proc_clk = 0, sync_clk = 0;
+  long long select_clk = 0;
   int n_selects = 0;
 #define QPB_STAMP(k) do { if (clk) clk[k] = clock64(); } while (0)
   QPB_STAMP(0);
@@ -410,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
   if (p.repeat_last_n >= 0 && hn > (long long)p.repeat_last_n) hfrom = hn - p.repeat_last_n;
   const int *hrow = a.history + (size_t)row * a.hist_stride;
   int first_id = -1;
-  if (use_pen) first_id = pen_prefetch(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn);
+  if (use_pen) first_id = pen_prefetch(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, S.pen_bloom);
 
   // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
   // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
@@ -441,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
     if (tid == 0)
       for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
   }
-  const int npen = use_pen ? pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status) : 0;
+  const int npen = use_pen ? pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom) : 0;
   QPB_STAMP(1);
   const bool greedy = p.temperature <= 0.f;
   const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
@@ -556,49 +568,39 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
         ++t;
         continue;
       }
-      const long long w0 = clk ? clock64() : 0;
       if (tile_bulk(t)) {
         if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g / kStages) & 1u)) failed = true;
       } else {  // unaligned row or ragged tail: plain loads into the same stage
         for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
         __syncthreads();
       }
-      const long long w1 = clk ? clock64() : 0;
       const int cnt_before = S.cand_count;  // settled: the previous tile ended with a barrier
       const bool slow = careful || thr != thr;
-      for (int half = 0; half < 2; ++half) {
-        const int hlen = min(kHalf, len - half * kHalf);  // columns of this half (uniform)
-        if (hlen <= 0) break;
-        const float *src = &S.ring[st][half * kHalf];
-        const float4 v0 = smem_load_f4(src + tid * 4);
-        const float4 v1 = smem_load_f4(src + kThreads * 4 + tid * 4);
-        const float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-        const int hbase = a.id_offset + tbase + half * kHalf;  // global id of the half's first column
+      for (int q = 0; q < kTile / kChunk; ++q) {
+        const int qlen = min(kChunk, len - q * kChunk);  // columns of this chunk (uniform)
+        if (qlen <= 0) break;
+        const float *src = &S.ring[st][q * kChunk];
+        const float4 v = smem_load_f4(src + tid * 4);
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        const int qbase = a.id_offset + tbase + q * kChunk;  // global id of the chunk's first column
         if (thr != thr) {
-          // no threshold yet: the whole half is taken, every column has its own slot, no atomics
+          // no threshold yet: the whole chunk is taken, every column has its own slot, no atomics
           const int cbase = S.cand_count;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
-            if (off < hlen && cbase + off < kCandCap) S.cand[cbase + off] = make_comp(f2key(f[e]), (uint32_t)(hbase + off));
+          for (int e = 0; e < 4; ++e) {
+            const int off = tid * 4 + e;
+            if (off < qlen && cbase + off < kCandCap) S.cand[cbase + off] = make_comp(f2key(f[e]), (uint32_t)(qbase + off));
           }
           __syncthreads();
-          if (tid == 0) S.cand_count = cbase + hlen;
+          if (tid == 0) S.cand_count = cbase + qlen;
         } else {
-          // one predicate per column; the bits of a ragged last half are masked by position
+          // one predicate per column; the bits of a ragged last chunk are masked by position
           uint32_t accmask = 0;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) accmask |= !(f[e] <= thr) ? (1u << e) : 0u;
-          if (hlen != kHalf) {
-            const int n0 = min(4, max(0, hlen - tid * 4)), n1 = min(4, max(0, hlen - kThreads * 4 - tid * 4));
-            accmask &= ((1u << n0) - 1u) | (((1u << n1) - 1u) << 4);
-          }
+          for (int e = 0; e < 4; ++e) accmask |= !(f[e] <= thr) ? (1u << e) : 0u;
+          if (qlen != kChunk) accmask &= (1u << min(4, max(0, qlen - tid * 4))) - 1u;
           const uint32_t lanes = __ballot_sync(0xffffffffu, accmask != 0u);
-          if (lanes != 0u) {
-            // Same-address shared-memory atomics serialise and warp votes are not free either: a warp with few
-            // survivors lets each of those lanes reserve its own slots, a warp with many reserves once for all
-            // of them and places them by a scan of the per-lane counts.  Survivors are re-read from the stage by
-            // position so that only they cost instructions.
+          if (lanes != 0u) {  // same slot reservation as on the fast path
             const int nacc = __popc(accmask);
             int pos;
             if (__popc(lanes) <= 6) {
@@ -607,8 +609,8 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
               int incl = nacc;
 #pragma unroll
               for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += v;
+                const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += t2;
               }
               int wbase = 0;
               if (lane == 31) wbase = smem_atomic_add(&S.cand_count, incl);
@@ -617,8 +619,8 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
             while (accmask) {
               const int e = __ffs(accmask) - 1;
               accmask &= accmask - 1u;
-              const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
-              if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(src[off]), (uint32_t)(hbase + off)));
+              const int off = tid * 4 + e;
+              if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(src[off]), (uint32_t)(qbase + off)));
               ++pos;
             }
           }
@@ -626,16 +628,14 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
         if (slow) {
           __syncthreads();
           const int c = S.cand_count;
-          if (c > kCandCap && tid == 0) atomicOr(a.status, ST_CAPACITY);  // cannot happen: c <= kCandHigh + kHalf
+          if (c > kCandCap && tid == 0) atomicOr(a.status, ST_CAPACITY);  // cannot happen: c <= kCandHigh + kChunk
           if (c > kCandHigh && c > M) shrink();
         }
       }
-      const long long w2 = clk ? clock64() : 0;
       __syncthreads();  // stage consumed by every thread; candidate count settled
-      if (clk) { const long long w3 = clock64(); wait_clk += w1 - w0; proc_clk += w2 - w1; sync_clk += w3 - w2; }
       const int cnt = S.cand_count;
       if (!slow && cnt > kCandCap) {
-        // more survivors than the list holds: forget this tile's, scan it again half by half
+        // more survivors than the list holds: forget this tile's, scan it again chunk by chunk
         __syncthreads();
         if (tid == 0) S.cand_count = cnt_before;
         careful = true;
@@ -662,7 +662,7 @@ __global__ void __launch_bounds__(kThreads, 3) stream_rows_kernel(const __grid_c
     __syncthreads();
   }
   QPB_STAMP(2);
-  if (clk) { clk[8] = select_clk; clk[9] = n_selects; clk[10] = S.cand_count; clk[11] = wait_clk; clk[12] = proc_clk; clk[13] = sync_clk; }
+  if (clk) { clk[8] = select_clk; clk[9] = n_selects; clk[10] = S.cand_count; }
   if (failed && tid == 0) atomicOr(a.status, ST_COPY_TIMEOUT);
 
   // MODE_MERGE: candidates come from the gathered per-shard lists instead of a stream

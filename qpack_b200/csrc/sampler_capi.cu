@@ -121,9 +121,8 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
 
 int pick_cluster(const qpb_sampler *s, int rows) {
   if (s->cluster) return s->cluster;
-  int c = 1;
-  while (c < 8 && (long long)rows * c < 2LL * s->sm_count) c <<= 1;
-  return c;
+  // one CTA per row as soon as a handful of rows are in flight; a cluster only pays for a few rows
+  return rows <= 8 ? 8 : 1;
 }
 
 template <int MODE>
@@ -264,27 +263,9 @@ int run_rows(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dis
     a.dist_p = d_dist_p;
     a.dist_count = d_dist_count;
     a.max_out = max_out;
-    // One CTA per row fills the GPU in waves of `slots` rows.  A last wave that would be less than half full is
-    // launched first, with its rows split over clusters of up to 8 CTAs so that it, too, covers every SM.
-    const int n = s->n_stream;
-    const int slots = s->stream_slots > 0 ? s->stream_slots : 3 * s->sm_count;
-    int head = 0, head_cluster = 1;
-    if (!s->cluster && n > slots) {
-      const int rem = n % slots;
-      if (rem > 0 && 2 * rem <= slots) {
-        head = rem;
-        head_cluster = slots / rem > 8 ? 8 : slots / rem;
-      }
-    }
-    if (head > 0) {
-      a.n_rows = head;
-      a.row_list = s->d_rows_stream;
-      rc = launch_stream<MODE_SAMPLE>(s, a, head, head_cluster, st);
-      if (rc) return rc;
-    }
-    a.n_rows = n - head;
-    a.row_list = s->d_rows_stream + head;
-    rc = launch_stream<MODE_SAMPLE>(s, a, n - head, head ? 1 : pick_cluster(s, n), st);
+    a.n_rows = s->n_stream;
+    a.row_list = s->d_rows_stream;
+    rc = launch_stream<MODE_SAMPLE>(s, a, s->n_stream, pick_cluster(s, s->n_stream), st);
     if (rc) return rc;
   }
   if (s->n_whole > 0) {
@@ -514,7 +495,7 @@ int qpb_sampler_cand_slots(qpb_sampler *s, int vocab_total, int vocab_local_max,
   long long m = 1;
   for (const auto &p : s->h_params) {
     long long b = row_budget(p, vocab_total);
-    if (b > kSmallMaxM) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 768");
+    if (b > kSmallMaxM) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 500");
     if (b >= vocab_total / 4) b = vocab_total;
     if (b > m) m = b;
   }
@@ -536,7 +517,7 @@ int qpb_sampler_local_candidates(qpb_sampler *s, const float *d_logits, int64_t 
   DeviceGuard g(s->device);
   rc = route_rows(s, n_rows, vocab_total, d_history ? hist_stride : 0, (cudaStream_t)stream);
   if (rc) return rc;
-  if (s->n_whole > 0) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 768");
+  if (s->n_whole > 0) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 500");
   StreamArgs a = {};
   fill_common(s, in, a);
   a.n_rows = n_rows;
@@ -560,7 +541,7 @@ int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_s
   DeviceGuard g(s->device);
   rc = route_rows(s, n_rows, vocab_total, d_history ? hist_stride : 0, (cudaStream_t)stream);
   if (rc) return rc;
-  if (s->n_whole > 0) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 768");
+  if (s->n_whole > 0) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 500");
   StreamArgs a = {};
   fill_common(s, in, a);
   a.n_rows = n_rows;
