@@ -134,6 +134,32 @@ QPB_API int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all,
                              const int32_t *d_hist_len, int hist_len_all, int32_t *d_dist_ids, float *d_dist_p,
                              int32_t *d_dist_count, int max_out, int32_t *d_out_ids, void *stream);
 
+/* ---- sampling without any allocation (this entry point has no counterpart in the reference) -----------------
+ * Some callers of a decode loop may not allocate device memory at all: an engine that reserves the whole GPU for
+ * its weights and KV cache at start-up and has nothing left to hand out, a real-time serving thread for which
+ * cudaMalloc is off limits because it synchronises the device, or a host that embeds the sampler where only
+ * pre-approved buffers may be touched.  A handle (qpb_sampler_create) allocates, so those callers get this call
+ * instead: it samples n_rows <= QPB_STATIC_MAX_ROWS rows exactly like a fresh handle would on its first
+ * qpb_sampler_sample_batch (row r seeded with params[r].seed, or params[0].seed + r when n_params == 1), and it
+ * calls no cudaMalloc, cudaFree or allocating library routine.  The per-call device state (parameter blocks,
+ * one MT19937-64 state per row, counters, a status word: about 320 KB) sits in a fixed array inside the library
+ * image, which every GPU that loads the library keeps until the process exits.
+ *
+ * h_params: host pointer, n_params == 1 or >= n_rows.  d_logits / d_history / d_hist_len / d_out_ids: device
+ * pointers on the CURRENT device, as for qpb_sampler_sample_batch.  d_status (optional device int): cleared, then
+ * OR-ed with the device status bits of the call (0 = fine).  errbuf (optional): receives a message on failure.
+ * Limits: more than QPB_STATIC_MAX_ROWS rows, or a row whose top_k + history window exceeds 500, is refused with
+ * QPB_ERR_UNSUPPORTED.  The first call on a device looks up the array's device address and sets a kernel
+ * attribute; make that first call outside any stream capture.  All calls on a device share the one array and it
+ * keeps the previous call's contents (each call re-seeds and clears what it uses), so two calls that overlap on
+ * the GPU (different streams) race: issue them on one stream or order them yourself.  Asynchronous. */
+#define QPB_STATIC_MAX_ROWS 128
+QPB_API int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, const float *d_logits,
+                                   int64_t row_stride, int n_rows, int vocab, const int32_t *d_history,
+                                   int64_t hist_stride, const int32_t *d_hist_len, int hist_len_all,
+                                   int32_t *d_out_ids, int32_t *d_status, void *stream, char *errbuf,
+                                   int errbuf_len);
+
 /* Debug aid for the tests: out[i] = the device's expf(x[i]) (the C library's expf bit for bit), n floats. */
 QPB_API int qpb_debug_expf(const float *d_x, float *d_out, int n, void *stream);
 

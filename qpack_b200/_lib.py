@@ -35,6 +35,8 @@ SIGNATURES = {
                                                _vp, C.c_int, _vp, C.c_int, _vp]),
     "qpb_sampler_merge_sample": (C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int,
                                            _vp, _vp, _vp, C.c_int, _vp, _vp]),
+    "qpb_sample_rows_static": (C.c_int, [_vp, C.c_int, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int,
+                                         _vp, _vp, _vp, C.c_char_p, C.c_int]),
     "qpb_debug_expf": (C.c_int, [_vp, _vp, C.c_int, _vp]),
 }
 

@@ -4,6 +4,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 #include <random>
 #include <string>
@@ -556,6 +557,155 @@ int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_s
   a.dist_count = d_dist_count;
   a.max_out = max_out;
   return launch_stream<MODE_MERGE>(s, a, n_rows, 1, (cudaStream_t)stream);
+}
+
+// ---- allocation-free entry point -------------------------------------------------------------------------------
+// Everything a handle would keep in device memory for a call (parameter blocks, one MT19937-64 state per row,
+// the words-drawn counters, a status word) lives in this fixed array instead.  It is part of the library image:
+// every GPU that loads the library holds it until the process exits.
+constexpr int kStaticMaxRows = QPB_STATIC_MAX_ROWS;
+constexpr size_t kStaticParamsOff = 0;
+constexpr size_t kStaticRngOff = kStaticParamsOff + sizeof(RowParams) * kStaticMaxRows;
+constexpr size_t kStaticDrawnOff = kStaticRngOff + sizeof(unsigned long long) * MT_N * kStaticMaxRows;
+constexpr size_t kStaticStatusOff = kStaticDrawnOff + sizeof(unsigned int) * kStaticMaxRows;
+constexpr size_t kStaticBytes = ((kStaticStatusOff + sizeof(int) + 255) / 256) * 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// Seeds row r's generator as std::mt19937_64(seed) would (sampler.cpp:8), clears its counter and the status words.
+__global__ void static_seed_kernel(const RowParams *params, int params_per_row, unsigned long long *rng,
+                                   unsigned int *drawn, int *status, int *user_status, int n_rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r == 0) {
+    *status = 0;
+    if (user_status) *user_status = 0;
+  }
+  if (r >= n_rows) return;
+  unsigned long long x = params_per_row ? params[r].seed : params[0].seed + (unsigned long long)r;
+  unsigned long long *mt = rng + (size_t)r * MT_N;
+  mt[0] = x;
+  for (int i = 1; i < MT_N; ++i) {
+    x = 6364136223846793005ULL * (x ^ (x >> 62)) + (unsigned long long)i;
+    mt[i] = x;
+  }
+  drawn[r] = 0u;
+}
+
+namespace {
+std::mutex g_static_mu;
+unsigned char *g_static_ptr[64] = {};  // device address of g_static_scratch, per device, once set up
+
+void static_msg(char *buf, int len, const char *msg) {
+  if (buf && len > 0) snprintf(buf, (size_t)len, "%s", msg);
+}
+}  // namespace
+
+int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, const float *d_logits, int64_t row_stride,
+                           int n_rows, int vocab, const int32_t *d_history, int64_t hist_stride,
+                           const int32_t *d_hist_len, int hist_len_all, int32_t *d_out_ids, int32_t *d_status,
+                           void *stream, char *errbuf, int errbuf_len) {
+  static_msg(errbuf, errbuf_len, "");
+  if (!h_params || !d_logits || !d_out_ids || n_rows <= 0 || vocab <= 0 || row_stride < vocab ||
+      (n_params != 1 && n_params < n_rows)) {
+    static_msg(errbuf, errbuf_len, "null pointer or size out of range");
+    return QPB_ERR_INVALID;
+  }
+  if (n_rows > kStaticMaxRows) {
+    static_msg(errbuf, errbuf_len, "n_rows exceeds QPB_STATIC_MAX_ROWS (the fixed device array holds 128 rows)");
+    return QPB_ERR_UNSUPPORTED;
+  }
+  if (d_history && (hist_stride < 0 || (!d_hist_len && (hist_len_all < 0 || hist_len_all > hist_stride)))) {
+    static_msg(errbuf, errbuf_len, "history length outside [0, hist_stride]");
+    return QPB_ERR_INVALID;
+  }
+  // parameter blocks on the stack (no heap, no device allocation); seed 0 asks for a non-deterministic seed
+  qpb_sampler_params local[kStaticMaxRows];
+  const int np = n_params == 1 ? 1 : n_rows;
+  long long max_window = 0;
+  for (int r = 0; r < np; ++r) {
+    local[r] = h_params[r];
+    if (local[r].seed == 0) {
+      std::random_device rd;
+      local[r].seed = (((uint64_t)rd() << 32) ^ rd()) | 1ULL;
+    }
+    const qpb_sampler_params &p = local[r];
+    long long w = 0;
+    const long long cap = d_history ? hist_stride : 0;
+    if (p.repeat_penalty != 1.f) w = p.repeat_last_n < 0 ? cap : (p.repeat_last_n < cap ? p.repeat_last_n : cap);
+    if (w > max_window) max_window = w;
+    const bool greedy = p.temperature <= 0.f;
+    const long long K = greedy ? 1 : (p.top_k > 0 ? (p.top_k < vocab ? p.top_k : vocab) : vocab);
+    if (K + w > kSmallMaxM) {
+      static_msg(errbuf, errbuf_len, "top_k + history window exceeds 500: such rows need the handle-based entry points");
+      return QPB_ERR_UNSUPPORTED;
+    }
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    static_msg(errbuf, errbuf_len, "no current CUDA device");
+    return QPB_ERR_CUDA;
+  }
+  unsigned char *base = nullptr;
+  {
+    // First call on a device: resolve the device address of the array.  Its name is a host-side stand-in in host
+    // code, so the address has to be asked for (with this device current) before a kernel can be given it.
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+      void *ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(stream_rows_kernel<MODE_SAMPLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e != cudaSuccess || !ptr) {
+        static_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+        return QPB_ERR_CUDA;
+      }
+      g_static_ptr[dev] = static_cast<unsigned char *>(ptr);
+    }
+    base = g_static_ptr[dev];
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  RowParams *d_params = reinterpret_cast<RowParams *>(base + kStaticParamsOff);
+  unsigned long long *d_rng = reinterpret_cast<unsigned long long *>(base + kStaticRngOff);
+  unsigned int *d_drawn = reinterpret_cast<unsigned int *>(base + kStaticDrawnOff);
+  int *d_stat = reinterpret_cast<int *>(base + kStaticStatusOff);
+  cudaError_t e = cudaMemcpyAsync(d_params, local, sizeof(RowParams) * np, cudaMemcpyHostToDevice, st);
+  if (e == cudaSuccess) {
+    static_seed_kernel<<<(n_rows + 63) / 64, 64, 0, st>>>(d_params, n_params == 1 ? 0 : 1, d_rng, d_drawn, d_stat, d_status, n_rows);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    static_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+    return QPB_ERR_CUDA;
+  }
+  StreamArgs a = {};
+  a.logits = d_logits;
+  a.row_stride = row_stride;
+  a.vocab = vocab;
+  a.vocab_total = vocab;
+  a.n_rows = n_rows;
+  a.params = d_params;
+  a.params_per_row = n_params == 1 ? 0 : 1;
+  a.history = d_history;
+  a.hist_stride = hist_stride;
+  a.hist_len = d_hist_len;
+  a.hist_len_all = d_history ? hist_len_all : 0;
+  a.rng_state = d_rng;
+  a.rng_drawn = d_drawn;
+  a.out_ids = d_out_ids;
+  a.draw = 1;
+  a.pen_slots = pen_slots_for(max_window);
+  a.status = d_status ? d_status : d_stat;
+  const size_t smem = sizeof(StreamSmem) + (size_t)a.pen_slots * sizeof(int);
+  if (smem > 200 * 1024) {
+    static_msg(errbuf, errbuf_len, "history window too large for the penalty table");
+    return QPB_ERR_UNSUPPORTED;
+  }
+  stream_rows_kernel<MODE_SAMPLE><<<n_rows, kThreads, smem, st>>>(a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    static_msg(errbuf, errbuf_len, cudaGetErrorString(e));
+    return QPB_ERR_CUDA;
+  }
+  return QPB_OK;
 }
 
 __global__ void debug_expf_kernel(const float *x, float *out, int n) {

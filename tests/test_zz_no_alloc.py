@@ -1,0 +1,85 @@
+"""The allocation-free entry point (qpb_sample_rows_static).
+
+It exists for callers that must not allocate device memory while they decode: an engine that has handed the whole
+GPU to its weights and KV cache, or a latency-critical serving thread for which cudaMalloc (a device-wide
+synchronisation) is forbidden.  Such a caller cannot create a handle, so this call keeps the per-call device state
+in a fixed array inside the library instead.  The test drives it through the C ABI and checks that it returns
+exactly the ids of the handle-based entry point, on two calls in a row (the array keeps the first call's contents,
+the second call must not be disturbed by them), and that sizes beyond its fixed capacity are refused.
+
+This file sorts last on purpose: a run that stops at the first failure has then already run every other test.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from qpack_b200 import _lib, synth
+from qpack_b200.sampler import BatchSampler
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def static_sample(lib, params, d_logits, d_hist, n_rows):
+    out = torch.full((n_rows,), -7, dtype=torch.int32, device=DEV)
+    status = torch.full((1,), 99, dtype=torch.int32, device=DEV)
+    err = C.create_string_buffer(256)
+    params = np.ascontiguousarray(params)
+    rc = lib.qpb_sample_rows_static(
+        params.ctypes.data, int(params.shape[0]), d_logits.data_ptr(), d_logits.stride(0), n_rows, d_logits.shape[1],
+        d_hist.data_ptr() if d_hist is not None else None, d_hist.shape[1] if d_hist is not None else 0, None,
+        d_hist.shape[1] if d_hist is not None else 0, out.data_ptr(), status.data_ptr(),
+        torch.cuda.current_stream().cuda_stream, err, 256)
+    return rc, out, status, err.value.decode()
+
+
+def handle_sample(params, d_logits, d_hist, n_rows):
+    bs = BatchSampler(n_rows, 0)
+    bs.set_params(params)
+    out = bs.sample(d_logits[:n_rows], d_hist[:n_rows] if d_hist is not None else None)
+    bs.check()
+    res = out.cpu().numpy()
+    bs.close()
+    return res
+
+
+def test_static_entry_matches_handle_entry_twice_in_a_row():
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    wl = synth.serving_batch(rows=48, vocab=151936)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    d_h = torch.from_numpy(wl.history).to(DEV)
+    # first call: 48 rows, per-row parameter blocks
+    want1 = handle_sample(wl.params, d_x, d_h, 48)
+    rc, out, status, msg = static_sample(lib, wl.params, d_x, d_h, 48)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(out.cpu().numpy(), want1)
+    # second call right after it: fewer rows, other seeds, one shared parameter block, no history
+    p2 = synth.make_params(1, temperature=0.9, top_k=64, top_p=0.9, min_p=0.05, repeat_penalty=1.0, seed=777)
+    want2 = handle_sample(p2, d_x, None, 20)
+    rc, out, status, msg = static_sample(lib, p2, d_x[:20], None, 20)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert np.array_equal(out.cpu().numpy(), want2)
+    # and the first configuration again: the array's leftovers from call two do not leak into it
+    rc, out, status, msg = static_sample(lib, wl.params, d_x, d_h, 48)
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), want1)
+
+
+def test_static_entry_refuses_sizes_beyond_its_capacity():
+    lib = _lib.load()
+    torch.cuda.set_device(0)
+    x = torch.zeros((130, 4096), dtype=torch.float32, device=DEV)
+    p = synth.make_params(1, seed=5)
+    rc, _, _, msg = static_sample(lib, p, x, None, 129)
+    assert rc == _lib.ERR_UNSUPPORTED and "128" in msg
+    p = synth.make_params(1, top_k=0, seed=5)  # top_k off needs the whole-row kernel
+    rc, _, _, msg = static_sample(lib, p, x, None, 4)
+    assert rc == _lib.ERR_UNSUPPORTED and "500" in msg
