@@ -1,0 +1,471 @@
+// The streaming sampler kernel proper (design notes at the top of sample_stream.cuh).
+//
+// A CTA works on PIECES: a piece is a run of whole tiles of one row.  Three ways of cutting rows into pieces:
+//   * one piece = one row (grid = rows);
+//   * a cluster of up to 8 CTAs per row, one piece per CTA, winners merged in the leader's shared memory (DSMEM):
+//     the low-latency path for a handful of rows;
+//   * persistent pieces (units_per_cta > 0): all tiles of all rows laid end to end and dealt out in equal runs
+//     to as many CTAs as fit on the GPU at once.  Every CTA gets the same number of tiles, so there is no last,
+//     partly filled wave, and neighbouring CTAs reach the compute-only phases at different times.  A row that
+//     straddles two CTAs leaves its pieces' winners in global scratch; the CTA that delivers the last piece merges
+//     them (a counter per row tells it so, nobody waits for anybody).
+// While streaming, a piece only needs an upper bound of the candidate budget (top_k + window length); the exact
+// budget (distinct ids of the window, sampler.cpp:32-41) is worked out by the CTA that finishes the row.
+#pragma once
+#include "sample_stream.cuh"
+
+namespace qpb {
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
+  int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int csize = (int)cluster.num_blocks();
+  const int crank = (int)cluster.block_rank();
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int Vt = a.vocab_total;
+  const uint32_t ring_s = smem_u32(&S.ring[0][0]), full_s = smem_u32(&S.full[0]);
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&S.full[s], 1);
+    mbar_fence_init();
+    S.cand_count = 0;
+  }
+  if (tid < 32) S.exp_tab[tid] = kExp2Tab[tid];
+  __syncthreads();
+
+  int g_next = 0;       // next free ring slot: slot g uses stage g % kStages on phase (g / kStages) & 1
+  bool failed = false;  // a bounded wait on a copy gave up
+
+  // ---- one piece: columns [s0, s1) of `row` (local columns of this GPU) ----------------------------------------
+  auto do_piece = [&](const int row, const int s0, const int s1, const int npieces, const int pi, long long *clk) {
+#define QPB_STAMP(k) do { if (clk) clk[k] = clock64(); } while (0)
+    QPB_STAMP(0);
+    long long select_clk = 0;
+    int n_selects = 0;
+    // independent global loads first, so that their latencies overlap
+    const RowParams p = a.params[a.params_per_row ? row : 0];
+    long long hn = (a.history == nullptr) ? 0 : (a.hist_len ? a.hist_len[row] : a.hist_len_all);
+    const float *rowp = a.logits + (size_t)row * a.row_stride;
+    const int n_tiles = (MODE == MODE_MERGE) ? 0 : (s1 - s0 + kTile - 1) / kTile;
+    const bool base_aligned = ((reinterpret_cast<uintptr_t>(rowp + s0) & 15u) == 0);
+
+    auto tile_len = [&](int t) { return min(kTile, s1 - s0 - t * kTile); };
+    auto tile_bulk = [&](int t) { return base_aligned && ((tile_len(t) & 3) == 0); };
+    auto issue = [&](int t, int g) {  // thread 0 only: tile t of the piece into ring slot g
+      if (t < n_tiles && tile_bulk(t)) {
+        const uint32_t bytes = (uint32_t)tile_len(t) * 4u;
+        uint64_t *bar = &S.full[g % kStages];
+        mbar_expect_tx(bar, bytes);
+        bulk_g2s(S.ring[g % kStages], rowp + s0 + (size_t)t * kTile, bytes, bar);
+      }
+    };
+    // Threshold bootstrap (long pieces only): the first kStages copies fetch tiles spread over the piece as a
+    // sample; a value that a chosen number of sampled columns reach becomes the first threshold, so that the
+    // stream itself only picks up about twice the columns it needs instead of filling the list several times.
+    // It is a guess: if fewer columns pass than are needed, the piece is streamed again without it.
+    const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kStages;
+    int g0 = g_next;  // ring slot of the piece's tile 0 (moved past the sample below)
+    if (tid == 0)
+      for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, g0 + j);
+
+    // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
+    MtFetch rng = {};
+    if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw)
+      rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+    // history window (sampler.cpp:32-35): "hn > (size_t)repeat_last_n ? hn - repeat_last_n : 0", so a negative
+    // repeat_last_n means the whole history
+    const bool use_pen = p.repeat_penalty != 1.f && a.history != nullptr;
+    hn = hn < 0 ? 0 : (hn > a.hist_stride ? a.hist_stride : hn);
+    long long hfrom = 0;
+    if (p.repeat_last_n >= 0 && hn > (long long)p.repeat_last_n) hfrom = hn - p.repeat_last_n;
+    const int *hrow = a.history + (size_t)row * a.hist_stride;
+    int first_id = -1;
+    if (use_pen && hfrom + tid < hn) first_id = hrow[hfrom + tid];
+
+    const bool greedy = p.temperature <= 0.f;
+    const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
+    // budget while streaming: an upper bound of K + |distinct window ids|; "whole row" as in top_m (sampler.cpp:14)
+    const long long wlen = use_pen ? hn - hfrom : 0;
+    int Mloc = (int)min((long long)Vt, (long long)K + wlen);
+    if (Mloc >= Vt / 4) Mloc = Vt;
+    const int need = min(Mloc, s1 - s0);  // columns this piece must deliver
+
+    // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
+    // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
+    // kernels_x86.cpp:509).  A NaN logit passes the test and is ordered below -inf by its key later.
+    float thr = __int_as_float(0x7fc00000);
+    bool booted = false;
+    if (can_boot) {
+      float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
+      for (int j = 0; j < kStages; ++j) {
+        const int g = g0 + j;
+        if (!mbar_wait_bounded(&S.full[g % kStages], (uint32_t)(g / kStages) & 1u)) failed = true;
+#pragma unroll
+        for (int h = 0; h < kTile / (kThreads * 4); ++h) {
+          const float4 v = *reinterpret_cast<const float4 *>(&S.ring[g % kStages][h * kThreads * 4 + tid * 4]);
+          const float f4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x = f4[e];  // NaN is ignored by fmaxf / fminf
+            m2 = fmaxf(m2, fminf(m1, x));
+            m1 = fmaxf(m1, x);
+          }
+        }
+      }
+      __syncthreads();  // the sample has been read by every thread
+      g0 += kStages;    // start the stream proper while the threshold is worked out (its tiles are fetched again)
+      if (tid == 0)
+        for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+      // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
+      const long long sample = (long long)kStages * kTile;
+      long long r = (9LL * Mloc * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
+      r = r < 16 ? 16 : r;
+      booted = Mloc < Vt && r <= 200;  // two maxima per thread hold the sample's best couple of hundred well enough
+      if (booted) {
+        S.cand[2 * tid] = make_comp(f2key(m1), (uint32_t)(2 * tid));
+        S.cand[2 * tid + 1] = make_comp(f2key(m2), (uint32_t)(2 * tid + 1));
+        __syncthreads();
+        const unsigned long long pivot = block_select_pivot(S.cand, 2 * kThreads, (int)r, S.hist, S.sel);
+        thr = key2f((uint32_t)(pivot >> 32));  // a lower bound of the r-th largest; key 0 gives NaN = no threshold
+        __syncthreads();                        // the list is free again
+      }
+    }
+    QPB_STAMP(1);
+
+    // keep the Mloc best of the list and raise the threshold to the weakest of them; all threads call it
+    auto shrink = [&]() {
+      const long long c0 = clk ? clock64() : 0;
+      block_keep_top(S.cand, min(S.cand_count, kCandCap), Mloc, S.hist, S.sel, &S.cand_count);
+      // later columns must beat the weakest kept key: an equal key at a higher index loses.  The select may stop
+      // on a key prefix, so take the minimum over the kept entries.
+      uint32_t mk = 0xffffffffu;
+      for (int i = tid; i < Mloc; i += kThreads) mk = min(mk, comp_key(S.cand[i]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mk = min(mk, __shfl_xor_sync(0xffffffffu, mk, o));
+      if (tid == 0) S.sel[3] = 0xffffffffu;
+      __syncthreads();
+      if (lane == 0) atomicMin(&S.sel[3], mk);
+      __syncthreads();
+      thr = key2f(S.sel[3]);  // key 1 (a NaN is among the kept) maps back to NaN: keep taking everything
+      if (clk) { select_clk += clock64() - c0; ++n_selects; }
+    };
+
+    // ---- streaming phase ----
+    // Fast mode scans a whole tile between two barriers and expects a handful of survivors.  Careful mode (no
+    // threshold yet, or a tile that overflowed the list in fast mode) scans a chunk of a tile at a time and
+    // selects whenever another chunk might not fit, so the list can never overflow whatever the data.
+    for (int attempt = 0; attempt < 2; ++attempt) {
+      bool careful = false;
+      for (int t = 0; t < n_tiles;) {
+        const int g = g0 + t;
+        const int st = g % kStages;
+        const int len = tile_len(t);
+        const int tbase = s0 + t * kTile;
+        if (!careful && thr == thr && len == kTile && base_aligned) {
+          // ---- fast tile: full, bulk-copied, threshold known.  Kept to a minimum of instructions: the scan is
+          // issue-latency bound with 8 warps per CTA. ----
+          const uint32_t bar = full_s + (uint32_t)st * 8u;
+          const uint32_t par = (uint32_t)(g / kStages) & 1u;
+          for (int polls = 0; !mbar_try_wait_addr(bar, par);)
+            if (++polls > (1 << 22)) { failed = true; break; }
+          const int cnt_before = S.cand_count;
+          const uint32_t stage_s = ring_s + (uint32_t)st * (kTile * 4u);
+          const uint32_t lane_s = stage_s + (uint32_t)tid * 16u;
+          uint32_t mask = 0;  // bit 4c + j: column c * 1024 + tid * 4 + j of the tile survives
+          mask_not_le<0>(lds_f4(lane_s), thr, mask);
+          mask_not_le<4>(lds_f4(lane_s + 4096u), thr, mask);
+          mask_not_le<8>(lds_f4(lane_s + 8192u), thr, mask);
+          mask_not_le<12>(lds_f4(lane_s + 12288u), thr, mask);
+          const uint32_t lanes = __ballot_sync(0xffffffffu, mask != 0u);
+          if (lanes != 0u) {
+            // Same-address shared-memory atomics serialise and a warp scan is not free either: a warp with few
+            // survivors lets each of those lanes reserve its own slots, a warp with many reserves once for all
+            // of them.  Survivors are re-read from the stage by position so that only they cost instructions.
+            const int nacc = __popc(mask);
+            int pos;
+            if (__popc(lanes) <= 6) {
+              pos = nacc ? smem_atomic_add(&S.cand_count, nacc) : 0;
+            } else {
+              int incl = nacc;
+#pragma unroll
+              for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+              }
+              int wbase = 0;
+              if (lane == 31) wbase = smem_atomic_add(&S.cand_count, incl);
+              pos = __shfl_sync(0xffffffffu, wbase, 31) + incl - nacc;
+            }
+            while (mask) {
+              const int e = __ffs(mask) - 1;
+              mask &= mask - 1u;
+              const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
+              if (pos < kCandCap)
+                smem_store_u64(&S.cand[pos], make_comp(f2key(lds_f32(stage_s + (uint32_t)off * 4u)),
+                                                        (uint32_t)(a.id_offset + tbase + off)));
+              ++pos;
+            }
+          }
+          __syncthreads();  // stage consumed by every thread; candidate count settled
+          const int cnt = S.cand_count;
+          if (cnt > kCandCap) {
+            // more survivors than the list holds: forget this tile's, scan it again chunk by chunk
+            __syncthreads();
+            if (tid == 0) S.cand_count = cnt_before;
+            careful = true;
+            if (cnt_before > kCandHigh && cnt_before > Mloc) { __syncthreads(); shrink(); }
+            __syncthreads();
+            continue;
+          }
+          if (tid == 0) issue(t + kStages, g + kStages);
+          if (cnt > kCandHighFast && cnt > Mloc) shrink();
+          ++t;
+          continue;
+        }
+        // ---- general tile: ragged, unaligned, no threshold yet, or careful mode ----
+        if (tile_bulk(t)) {
+          if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g / kStages) & 1u)) failed = true;
+        } else {  // unaligned row or ragged tail: plain loads into the same stage
+          for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
+          if (tid == 0) mbar_arrive(&S.full[st]);  // nobody waits on it, but the slot's phase has to advance
+          __syncthreads();
+        }
+        const int cnt_before = S.cand_count;  // settled: the previous tile ended with a barrier
+        const bool slow = careful || thr != thr;
+        for (int q = 0; q < kTile / kChunk; ++q) {
+          const int qlen = min(kChunk, len - q * kChunk);  // columns of this chunk (uniform)
+          if (qlen <= 0) break;
+          const float *src = &S.ring[st][q * kChunk];
+          const float4 v = smem_load_f4(src + tid * 4);
+          const float f[4] = {v.x, v.y, v.z, v.w};
+          const int qbase = a.id_offset + tbase + q * kChunk;  // global id of the chunk's first column
+          if (thr != thr) {
+            // no threshold yet: the whole chunk is taken, every column has its own slot, no atomics
+            const int cbase = S.cand_count;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int off = tid * 4 + e;
+              if (off < qlen && cbase + off < kCandCap) S.cand[cbase + off] = make_comp(f2key(f[e]), (uint32_t)(qbase + off));
+            }
+            __syncthreads();
+            if (tid == 0) S.cand_count = cbase + qlen;
+          } else {
+            // one predicate per column; the bits of a ragged last chunk are masked by position
+            uint32_t accmask = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) accmask |= !(f[e] <= thr) ? (1u << e) : 0u;
+            if (qlen != kChunk) accmask &= (1u << min(4, max(0, qlen - tid * 4))) - 1u;
+            const uint32_t lanes = __ballot_sync(0xffffffffu, accmask != 0u);
+            if (lanes != 0u) {  // same slot reservation as on the fast path
+              const int nacc = __popc(accmask);
+              int pos;
+              if (__popc(lanes) <= 6) {
+                pos = nacc ? smem_atomic_add(&S.cand_count, nacc) : 0;
+              } else {
+                int incl = nacc;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                  const int t2 = __shfl_up_sync(0xffffffffu, incl, o);
+                  if (lane >= o) incl += t2;
+                }
+                int wbase = 0;
+                if (lane == 31) wbase = smem_atomic_add(&S.cand_count, incl);
+                pos = __shfl_sync(0xffffffffu, wbase, 31) + incl - nacc;
+              }
+              while (accmask) {
+                const int e = __ffs(accmask) - 1;
+                accmask &= accmask - 1u;
+                const int off = tid * 4 + e;
+                if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(src[off]), (uint32_t)(qbase + off)));
+                ++pos;
+              }
+            }
+          }
+          if (slow) {
+            __syncthreads();
+            const int c = S.cand_count;
+            if (c > kCandCap && tid == 0) atomicOr(a.status, ST_CAPACITY);  // cannot happen: c <= kCandHigh + kChunk
+            if (c > kCandHigh && c > Mloc) shrink();
+          }
+        }
+        __syncthreads();  // stage consumed by every thread; candidate count settled
+        const int cnt = S.cand_count;
+        if (!slow && cnt > kCandCap) {
+          // more survivors than the list holds: forget this tile's, scan it again chunk by chunk
+          __syncthreads();
+          if (tid == 0) S.cand_count = cnt_before;
+          careful = true;
+          if (cnt_before > kCandHigh && cnt_before > Mloc) { __syncthreads(); shrink(); }
+          __syncthreads();
+          continue;
+        }
+        if (tid == 0) issue(t + kStages, g + kStages);
+        if (!slow && cnt > kCandHighFast && cnt > Mloc) shrink();
+        ++t;
+      }
+      g0 += n_tiles;  // every slot up to here has been issued and consumed
+      // every column above the bootstrap threshold was collected; with at least `need` of them the needed ones
+      // are all in the list.  Otherwise the guess was too high: stream the piece once more from "no threshold".
+      if (!booted || S.cand_count >= need) break;
+      __syncthreads();
+      booted = false;
+      thr = __int_as_float(0x7fc00000);
+      if (tid == 0) {
+        S.cand_count = 0;
+        for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+      }
+      if (clk) clk[14] += 1;
+      __syncthreads();
+    }
+    g_next = g0;
+    QPB_STAMP(2);
+    if (clk) { clk[8] = select_clk; clk[9] = n_selects; clk[10] = S.cand_count; }
+    if (failed && tid == 0) atomicOr(a.status, ST_COPY_TIMEOUT);
+
+    // MODE_MERGE: candidates come from the gathered per-shard lists instead of a stream
+    if (MODE == MODE_MERGE) {
+      const int total = a.n_shards * a.cand_slots;
+      for (int i0 = 0; i0 < total; i0 += kThreads) {  // uniform trip count: every lane votes
+        const int i = i0 + tid;
+        unsigned long long c = 0ULL;
+        if (i < total) {
+          const int sh = i / a.cand_slots, sl = i - sh * a.cand_slots;
+          c = a.cand_io[((size_t)sh * a.cand_rows + row) * a.cand_slots + sl];
+        }
+        const uint32_t m = __ballot_sync(0xffffffffu, c != 0ULL);
+        int wbase = 0;
+        if (lane == 0 && m) wbase = atomicAdd(&S.cand_count, __popc(m));
+        wbase = __shfl_sync(0xffffffffu, wbase, 0);
+        const int pos = wbase + __popc(m & ((1u << lane) - 1u));
+        if (c != 0ULL && pos < kMergeCap) S.cand[pos] = c;
+      }
+      __syncthreads();
+      if (S.cand_count > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
+    }
+
+    int n = min(S.cand_count, MODE == MODE_MERGE ? kMergeCap : kCandCap);
+    // Lists that travel (cluster merge, piece scratch, all-gather) are cut to the streaming budget first.
+    const bool travels = csize > 1 || npieces > 1 || MODE != MODE_SAMPLE;
+    if (travels) n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
+    QPB_STAMP(3);
+
+    if (csize > 1) {
+      // ---- cluster merge: every CTA pushes its winners into the leader's list over DSMEM ----
+      cluster.sync();  // the leader's ring is idle and its own list is final
+      if (crank != 0) {
+        StreamSmem *L = cluster.map_shared_rank(&S, 0);
+        if (tid == 0) S.misc[0] = atomicAdd(&L->cand_count, n);
+        __syncthreads();
+        const int base = S.misc[0];
+        for (int i = tid; i < n; i += kThreads)
+          if (base + i < kMergeCap) L->cand[base + i] = S.cand[i];
+        if (base + n > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
+      }
+      cluster.sync();
+      if (crank != 0) return;
+      n = min(S.cand_count, kMergeCap);
+      n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
+    } else if (npieces > 1) {
+      // ---- row in pieces: leave this piece's winners in scratch; whoever delivers the last piece finishes ----
+      const int slot_row = a.units_per_cta > 0 ? row : 0;  // scratch is indexed by row
+      unsigned long long *mine = a.piece_cand + ((size_t)slot_row * a.max_pieces + pi) * kSmallMaxM;
+      for (int i = tid; i < n; i += kThreads) mine[i] = S.cand[i];
+      if (tid == 0) a.piece_cnt[(size_t)slot_row * a.max_pieces + pi] = n;
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();  // the list is visible before the counter moves
+        const int before = atomicAdd(&a.piece_done[slot_row], 1);
+        S.misc[0] = before;
+        if (before + 1 == npieces) {
+          a.piece_done[slot_row] = 0;  // every other piece has checked in: ready for the next launch
+          __threadfence();             // and their lists may be read
+        }
+      }
+      __syncthreads();
+      if (S.misc[0] + 1 != npieces) {  // not the last piece: the next piece starts with an empty list
+        __syncthreads();
+        if (tid == 0) S.cand_count = 0;
+        __syncthreads();
+        return;
+      }
+      for (int q = 0; q < npieces; ++q) {
+        if (q == pi) continue;
+        const unsigned long long *src = a.piece_cand + ((size_t)slot_row * a.max_pieces + q) * kSmallMaxM;
+        const int cq = __ldcg(&a.piece_cnt[(size_t)slot_row * a.max_pieces + q]);
+        for (int i = tid; i < cq; i += kThreads)
+          if (n + i < kMergeCap) S.cand[n + i] = __ldcg(&src[i]);
+        n += cq;
+      }
+      if (n > kMergeCap) { if (tid == 0) atomicOr(a.status, ST_CAPACITY); n = kMergeCap; }
+      __syncthreads();
+      n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
+    }
+    QPB_STAMP(4);
+
+    if (MODE == MODE_LOCAL_TOPM) {  // hand this GPU's winners to the all-gather
+      unsigned long long *out = a.cand_io + (size_t)row * a.cand_slots;
+      for (int i = tid; i < a.cand_slots; i += kThreads) out[i] = i < n ? S.cand[i] : 0ULL;
+      if (n > a.cand_slots && tid == 0) atomicOr(a.status, ST_CAPACITY);
+      __syncthreads();
+      if (tid == 0) S.cand_count = 0;
+      __syncthreads();
+      return;
+    }
+
+    // ---- this CTA finishes the row: exact budget from the distinct window ids (sampler.cpp:32-41) ----
+    int npen = 0;
+    if (use_pen) {
+      pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
+      __syncthreads();
+      npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
+    }
+    int M = min(Vt, K + npen);
+    if (M >= Vt / 4) M = Vt;  // top_m returns the whole row in this case (sampler.cpp:14)
+    // The reference penalises exactly its M largest raw entries.  When the penalty only lowers values
+    // (repeat_penalty >= 1) the K best after the penalty are the same over any superset of those M, so the exact
+    // raw cut can be skipped; a penalty below 1 raises values and needs it.
+    if (npen > 0 && !(p.repeat_penalty >= 1.f)) n = block_keep_top(S.cand, n, M, S.hist, S.sel, &S.cand_count);
+
+    unsigned long long *sorted = reinterpret_cast<unsigned long long *>(&S.ring[0][0]);
+    float *ev = reinterpret_cast<float *>(&S.cand[0]);
+    float *pv = ev + kCandCap;
+    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, rng, clk);
+    QPB_STAMP(7);
+    __syncthreads();  // the ring (sorted) and the list are free for the next piece
+    if (tid == 0) S.cand_count = 0;
+    __syncthreads();
+#undef QPB_STAMP
+  };  // do_piece
+
+  if (a.units_per_cta > 0) {
+    // persistent pieces: CTA b owns the tiles [b * Q, (b + 1) * Q) of the rows laid end to end
+    const long long Q = a.units_per_cta, tpr = a.tiles_per_row;
+    const long long total = (long long)a.n_rows * tpr;
+    const long long u0 = (long long)blockIdx.x * Q, u1 = min(total, u0 + Q);
+    for (long long u = u0; u < u1;) {
+      const long long r = u / tpr;
+      const int t0 = (int)(u - r * tpr), t1 = (int)min(tpr, u1 - r * tpr);
+      const long long first = (r * tpr) / Q, last = ((r + 1) * tpr - 1) / Q;
+      const int row = a.row_list ? a.row_list[r] : (int)r;
+      do_piece(row, min(a.vocab, t0 * kTile), min(a.vocab, t1 * kTile), (int)(last - first + 1),
+               (int)((long long)blockIdx.x - first), nullptr);
+      u = r * tpr + t1;
+    }
+  } else {
+    // one row per cluster: this CTA's slice, cut at multiples of 4 floats to keep 16-byte alignment
+    const int slot = blockIdx.x / csize;
+    const int row = a.row_list ? a.row_list[slot] : slot;
+    int per = (a.vocab + csize - 1) / csize;
+    per = (per + 3) & ~3;
+    const int s0 = min(a.vocab, crank * per), s1 = min(a.vocab, s0 + per);
+    long long *clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
+    if (clk) { clk[11] = 0; clk[12] = 0; clk[13] = 0; clk[14] = 0; clk[15] = 0; }
+    do_piece(row, s0, s1, 1, 0, clk);
+  }
+}
+
+}  // namespace qpb

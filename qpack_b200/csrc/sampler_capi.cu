@@ -11,7 +11,7 @@
 #include <vector>
 
 #include "../../include/qpack_b200_sampler.h"
-#include "sample_stream.cuh"
+#include "sample_stream_kernel.cuh"
 #include "sample_whole_kernel.cuh"
 
 using namespace qpb;
@@ -46,6 +46,11 @@ struct qpb_sampler {
   int *d_stage_ids = nullptr;
   cudaStream_t own_stream = nullptr;
   long long *d_phase_clk = nullptr;  // [max_rows][16] when phase stamps are enabled
+  // scratch of the persistent-piece schedule: winners of row pieces, their counts, pieces delivered per row
+  unsigned long long *d_piece_cand = nullptr;
+  int *d_piece_cnt = nullptr, *d_piece_done = nullptr;
+  int piece_cap = 0;  // pieces per row the scratch holds
+  int pieces = 1;     // 1: rows may be cut into pieces (default), 0: never
   std::string err;
 };
 
@@ -124,6 +129,49 @@ int pick_cluster(const qpb_sampler *s, int rows) {
   if (s->cluster) return s->cluster;
   // one CTA per row as soon as a handful of rows are in flight; a cluster only pays for a few rows
   return rows <= 8 ? 8 : 1;
+}
+
+template <int MODE>
+int launch_stream(qpb_sampler *s, const StreamArgs &args, int ctas, int cluster, cudaStream_t st);
+
+// Cuts the rows of a launch into persistent pieces when that pays: fills the piece fields of `a` and returns the
+// number of CTAs to launch (0: keep one row per CTA / cluster).
+int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas) {
+  *ctas = 0;
+  if (!s->pieces || s->cluster || s->d_phase_clk || n_rows < 2) return QPB_OK;
+  const int slots = s->stream_slots > 0 ? s->stream_slots : 4 * s->sm_count;
+  const long long tpr = (a.vocab + kTile - 1) / kTile;
+  const long long total = (long long)n_rows * tpr;
+  const long long min_units = 12;  // shorter pieces cannot bootstrap a threshold
+  if (tpr < min_units) return QPB_OK;
+  long long G = total / min_units < slots ? total / min_units : slots;
+  if (G < 1) G = 1;
+  const long long Q = (total + G - 1) / G;
+  G = (total + Q - 1) / Q;
+  const int max_pieces = (int)((tpr + Q - 1) / Q) + 1;
+  if ((long long)max_pieces * kSmallMaxM > kMergeCap) return QPB_OK;
+  if (max_pieces > s->piece_cap) {
+    QPB_CUDA(s, cudaDeviceSynchronize());
+    cudaFree(s->d_piece_cand);
+    cudaFree(s->d_piece_cnt);
+    cudaFree(s->d_piece_done);
+    s->d_piece_cand = nullptr;
+    s->d_piece_cnt = s->d_piece_done = nullptr;
+    s->piece_cap = 0;
+    QPB_CUDA(s, cudaMalloc(&s->d_piece_cand, sizeof(unsigned long long) * kSmallMaxM * (size_t)max_pieces * s->max_rows));
+    QPB_CUDA(s, cudaMalloc(&s->d_piece_cnt, sizeof(int) * (size_t)max_pieces * s->max_rows));
+    QPB_CUDA(s, cudaMalloc(&s->d_piece_done, sizeof(int) * (size_t)s->max_rows));
+    QPB_CUDA(s, cudaMemset(s->d_piece_done, 0, sizeof(int) * (size_t)s->max_rows));
+    s->piece_cap = max_pieces;
+  }
+  a.units_per_cta = (int)Q;
+  a.tiles_per_row = (int)tpr;
+  a.max_pieces = s->piece_cap;
+  a.piece_cand = s->d_piece_cand;
+  a.piece_cnt = s->d_piece_cnt;
+  a.piece_done = s->d_piece_done;
+  *ctas = (int)G;
+  return QPB_OK;
 }
 
 template <int MODE>
@@ -266,7 +314,11 @@ int run_rows(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dis
     a.max_out = max_out;
     a.n_rows = s->n_stream;
     a.row_list = s->d_rows_stream;
-    rc = launch_stream<MODE_SAMPLE>(s, a, s->n_stream, pick_cluster(s, s->n_stream), st);
+    int ctas = 0;
+    rc = plan_pieces(s, a, s->n_stream, &ctas);
+    if (rc) return rc;
+    if (ctas > 0) rc = launch_stream<MODE_SAMPLE>(s, a, ctas, 1, st);
+    else rc = launch_stream<MODE_SAMPLE>(s, a, s->n_stream, pick_cluster(s, s->n_stream), st);
     if (rc) return rc;
   }
   if (s->n_whole > 0) {
@@ -327,6 +379,9 @@ int qpb_sampler_destroy(qpb_sampler *s) {
   cudaFree(s->d_stage_hlen);
   cudaFree(s->d_stage_ids);
   cudaFree(s->d_phase_clk);
+  cudaFree(s->d_piece_cand);
+  cudaFree(s->d_piece_cnt);
+  cudaFree(s->d_piece_done);
   whole_free(s);
   if (s->own_stream) cudaStreamDestroy(s->own_stream);
   delete s;
