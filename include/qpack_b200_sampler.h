@@ -104,6 +104,11 @@ QPB_API int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state
 /* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1 to 8. */
 QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
 
+/* Row pieces: the tiles of all rows of a call laid end to end and dealt out in equal runs to as many CTAs as fit on
+ * the GPU, rows that straddle two CTAs merged through device scratch (allocated on first use).  mode 0 (default):
+ * only when whole rows would leave the last wave of CTAs less than a quarter full; 1: always; -1: never. */
+QPB_API int qpb_sampler_set_pieces(qpb_sampler *s, int mode);
+
 /* Latency breakdown aid.  enable != 0 turns on per-row phase stamps (SM clock of the row's leader CTA:
  * [0] start, [1] penalty set built, [2] row streamed, [3] exact candidate set, [4] cluster merge done,
  * [5] candidates ordered, [6] softmax numerators, [7] end; [8] clocks spent in selects while streaming,

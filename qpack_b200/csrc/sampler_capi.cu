@@ -50,7 +50,7 @@ struct qpb_sampler {
   unsigned long long *d_piece_cand = nullptr;
   int *d_piece_cnt = nullptr, *d_piece_done = nullptr;
   int piece_cap = 0;  // pieces per row the scratch holds
-  int pieces = 1;     // 1: rows may be cut into pieces (default), 0: never
+  int pieces = 0;     // row pieces: 0 automatic (only when the last wave of whole rows would be nearly empty), 1 always, -1 never
   std::string err;
 };
 
@@ -138,8 +138,11 @@ int launch_stream(qpb_sampler *s, const StreamArgs &args, int ctas, int cluster,
 // number of CTAs to launch (0: keep one row per CTA / cluster).
 int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas) {
   *ctas = 0;
-  if (!s->pieces || s->cluster || s->d_phase_clk || n_rows < 2) return QPB_OK;
+  if (s->pieces < 0 || s->cluster || s->d_phase_clk || n_rows < 2) return QPB_OK;
   const int slots = s->stream_slots > 0 ? s->stream_slots : 4 * s->sm_count;
+  // Pieces cost a threshold bootstrap, a cut and a trip through scratch each, so whole rows win unless their last
+  // wave would leave most of the GPU idle.
+  if (s->pieces == 0 && (n_rows <= slots || (n_rows % slots) * 4 > slots || n_rows % slots == 0)) return QPB_OK;
   const long long tpr = (a.vocab + kTile - 1) / kTile;
   const long long total = (long long)n_rows * tpr;
   const long long min_units = 12;  // shorter pieces cannot bootstrap a threshold
@@ -518,6 +521,13 @@ int qpb_sampler_set_cluster(qpb_sampler *s, int cluster) {
   if (!s) return QPB_ERR_INVALID;
   if (cluster < 0 || cluster > 8) return fail(s, QPB_ERR_INVALID, "cluster must be 0 (automatic) or 1..8");
   s->cluster = cluster;
+  return QPB_OK;
+}
+
+int qpb_sampler_set_pieces(qpb_sampler *s, int mode) {
+  if (!s) return QPB_ERR_INVALID;
+  if (mode < -1 || mode > 1) return fail(s, QPB_ERR_INVALID, "mode must be -1, 0 or 1");
+  s->pieces = mode;
   return QPB_OK;
 }
 

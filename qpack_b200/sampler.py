@@ -82,6 +82,10 @@ class BatchSampler:
     def set_cluster(self, cluster: int):
         self._ck(self._lib.qpb_sampler_set_cluster(self._h, int(cluster)))
 
+    def set_pieces(self, mode: int):
+        """Row pieces: 0 automatic, 1 always, -1 never (see qpb_sampler_set_pieces)."""
+        self._ck(self._lib.qpb_sampler_set_pieces(self._h, int(mode)))
+
     def _stream(self, stream):
         if stream is None:
             stream = torch.cuda.current_stream(self._tdev)

@@ -135,6 +135,25 @@ def test_config_rows(name, rows, cluster):
     assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, rep
 
 
+@pytest.mark.parametrize("rows", [7, 96, 700])
+def test_rows_in_pieces(rows):
+    """Row pieces forced on: rows straddle CTAs, piece winners meet in device scratch, the last arriver finishes.
+    Results must not depend on the schedule; a second call reuses the self-resetting piece counters."""
+    wl = synth.serving_batch(rows=rows)
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    d_x = torch.from_numpy(wl.logits).to(DEV)
+    d_h = torch.from_numpy(wl.history).to(DEV)
+    bs = BatchSampler(rows, 0)
+    bs.set_pieces(1)
+    for _ in range(2):
+        bs.set_params(wl.params)
+        ids, p, cnt, out = bs.dist(d_x, d_h, None, max_out=64, draw=True)
+        bs.check()
+        rep = compare_rows(out.cpu().numpy(), cnt.cpu().numpy(), ids.cpu().numpy(), p.cpu().numpy(), exp)
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, rep
+    bs.close()
+
+
 def test_unaligned_rows_take_the_plain_load_path():
     """Row stride and base not multiples of 16 bytes: the bulk-copy path is not usable, results are the same."""
     wl = synth.serving_batch(rows=6, vocab=30001)
