@@ -1,0 +1,104 @@
+// C++17 mirror of the reference sampler interface (qp::SamplerParams / qp::Sampler, include/qpack/engine.h:17-43)
+// on top of the C ABI of qpack_b200_sampler.h: same names, signatures, defaults and error convention (a failing
+// call throws std::runtime_error, as the engine does: src/chat.cpp:105-106).  Header-only; link with
+// libqpack_b200_sampler.so.  Code written against qp::Sampler compiles against qpb::Sampler unchanged.
+#pragma once
+#include <algorithm>
+#include <cstddef>
+#include <cstdint>
+#include <stdexcept>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../qpack_b200_sampler.h"
+
+namespace qpb {
+
+struct SamplerParams {          // engine.h:17-25
+  float temperature = 0.7f;     // <= 0: greedy
+  int top_k = 40;               // 0: off
+  float top_p = 0.9f;           // 1: off
+  float min_p = 0.05f;          // 0: off (relative to the top probability)
+  float repeat_penalty = 1.1f;
+  int repeat_last_n = 64;
+  uint64_t seed = 0;            // 0: random
+};
+static_assert(sizeof(SamplerParams) == sizeof(qpb_sampler_params), "same block as the C ABI");
+
+class Sampler {
+ public:
+  explicit Sampler(const SamplerParams &p, int device = 0) : p_(p) {  // engine.h:29, src/sampler.cpp:8
+    if (qpb_sampler_create(&h_, device, 1) != QPB_OK) throw std::runtime_error("qpb_sampler_create failed (no sm_100 GPU?)");
+    qpb_sampler_params q{p.temperature, p.top_k, p.top_p, p.min_p, p.repeat_penalty, p.repeat_last_n, p.seed};
+    check(qpb_sampler_set_params(h_, &q, 1));
+  }
+  ~Sampler() { qpb_sampler_destroy(h_); }
+  Sampler(const Sampler &) = delete;
+  Sampler &operator=(const Sampler &) = delete;
+
+  // engine.h:30.  `logits` is a host pointer, as every qp::Model::step returns it (include/qpack/qpack.h:137).
+  int sample(const float *logits, int vocab, const std::vector<int> &history) {
+    int id = -1;
+    check(qpb_sampler_sample_host(h_, logits, vocab, 1, vocab, hist_ptr(history), (int64_t)history.size(), nullptr,
+                                  (int)history.size(), &id));
+    return id;
+  }
+  // engine.h:31-34: (token, probability) pairs summing to 1, most likely first; `hist_len` limits the history to
+  // its first entries.
+  void dist(const float *logits, int vocab, const std::vector<int> &history, std::vector<std::pair<int, float>> &out,
+            size_t hist_len = (size_t)-1) {
+    const size_t hn = hist_len < history.size() ? hist_len : history.size();
+    int cap = p_.temperature <= 0 ? 1 : (p_.top_k > 0 && p_.top_k < vocab ? p_.top_k : vocab);
+    ids_.resize((size_t)cap);
+    pr_.resize((size_t)cap);
+    int count = 0;
+    check(qpb_sampler_dist_host(h_, logits, vocab, 1, vocab, hist_ptr(history), (int64_t)history.size(), nullptr,
+                                (int)hn, ids_.data(), pr_.data(), &count, cap, nullptr));
+    out.clear();
+    for (int i = 0; i < count && i < cap; i++) out.push_back({ids_[(size_t)i], pr_[(size_t)i]});
+    // rows with a large budget (top_k off) come back unordered from the whole-row kernel: most likely first
+    if (cap > 500)
+      std::sort(out.begin(), out.end(), [](const std::pair<int, float> &a, const std::pair<int, float> &b) {
+        return a.second > b.second || (a.second == b.second && a.first < b.first);
+      });
+  }
+  // engine.h:35, src/sampler.cpp:58-63: one entry takes no random number
+  int draw(const std::vector<std::pair<int, float>> &d) {
+    if (d.size() == 1) return d[0].first;
+    double r = uniform();
+    for (auto &c : d) { r -= c.second; if (r <= 0) return c.first; }
+    return d.back().first;
+  }
+  // engine.h:36-39, src/sampler.cpp:65-73: speculative step for a proposed token
+  bool accept(const std::vector<std::pair<int, float>> &d, int token, int *repl) {
+    float p = 0;
+    for (auto &c : d) if (c.first == token) { p = c.second; break; }
+    if (p >= 1.f) return true;
+    if (p > 0 && uniform() < p) return true;
+    std::vector<std::pair<int, float>> rest;
+    rest.reserve(d.size());
+    for (auto &c : d) if (c.first != token) rest.push_back({c.first, c.second / (1.f - p)});
+    *repl = rest.empty() ? token : draw(rest);
+    return false;
+  }
+  const SamplerParams &params() const { return p_; }
+  qpb_sampler *handle() { return h_; }  // for the batch / device-pointer entry points of the C ABI
+
+ private:
+  static const int *hist_ptr(const std::vector<int> &h) { return h.empty() ? nullptr : h.data(); }
+  double uniform() {  // the next variate of the sampler's own MT19937-64 stream, kept on the device
+    double u = 0;
+    check(qpb_sampler_next_uniform(h_, 0, &u));
+    return u;
+  }
+  void check(int rc) {
+    if (rc != QPB_OK) throw std::runtime_error(std::string("qpack_b200 sampler: ") + qpb_sampler_last_error(h_));
+  }
+  SamplerParams p_;
+  qpb_sampler *h_ = nullptr;
+  std::vector<int> ids_;
+  std::vector<float> pr_;
+};
+
+}  // namespace qpb

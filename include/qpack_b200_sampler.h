@@ -93,6 +93,19 @@ QPB_API int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64
                             const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len,
                             int hist_len_all, int32_t *h_out_ids);
 
+/* qp::Sampler::dist (and draw, when h_out_ids is not NULL) with host buffers in and out, as the reference's
+ * callers hold them (src/chat.cpp:211,238).  Synchronous. */
+QPB_API int qpb_sampler_dist_host(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
+                                  const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len,
+                                  int hist_len_all, int32_t *h_dist_ids, float *h_dist_p, int32_t *h_dist_count,
+                                  int max_out, int32_t *h_out_ids);
+
+/* The next uniform variate of row `row`'s RNG stream, exactly what
+ * std::uniform_real_distribution<double>(0, 1)(rng_) returns in qp::Sampler::draw / accept (src/sampler.cpp:60,68);
+ * the stream advances by one word.  Lets a host-side draw() / accept() on (id, probability) pairs share the
+ * stream with the device-side draws.  Synchronous. */
+QPB_API int qpb_sampler_next_uniform(qpb_sampler *s, int row, double *h_u);
+
 /* Synchronises `stream`, reads and clears the device status word of the calls issued so far. */
 QPB_API int qpb_sampler_check(qpb_sampler *s, void *stream);
 

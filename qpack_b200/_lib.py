@@ -23,6 +23,9 @@ SIGNATURES = {
     "qpb_sampler_dist_batch": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp, _vp,
                                          _vp, C.c_int, _vp, _vp]),
     "qpb_sampler_sample_host": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp]),
+    "qpb_sampler_dist_host": (C.c_int, [_vp, _vp, C.c_int64, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int, _vp, _vp,
+                                        _vp, C.c_int, _vp]),
+    "qpb_sampler_next_uniform": (C.c_int, [_vp, C.c_int, C.POINTER(C.c_double)]),
     "qpb_sampler_check": (C.c_int, [_vp, _vp]),
     "qpb_sampler_rng_get": (C.c_int, [_vp, C.c_int, _vp]),
     "qpb_sampler_rng_set": (C.c_int, [_vp, C.c_int, _vp]),

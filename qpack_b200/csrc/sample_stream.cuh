@@ -242,7 +242,7 @@ __device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int 
 // (kCandCap floats each) may alias cand, which is dead once `sorted` is written.
 __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
                            const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv,
-                           StreamSmem &S, const MtFetch &rng, long long *clk) {
+                           StreamSmem &S, long long *clk) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied
   if (npen > 0) {
@@ -335,7 +335,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   int pick = 0;
   if (keep > 1 && a.draw) {
     unsigned long long w = 0;
-    if (lane == 0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+    if (lane == 0) w = mt_next(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
     w = __shfl_sync(0xffffffffu, w, 0);
     double r = word_to_uniform(w);
     pick = keep - 1;

@@ -16,7 +16,7 @@
 
 namespace qpb {
 
-template <int MODE>
+template <int MODE, bool TIMED = false>
 __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
@@ -41,7 +41,8 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
   bool failed = false;  // a bounded wait on a copy gave up
 
   // ---- one piece: columns [s0, s1) of `row` (local columns of this GPU) ----------------------------------------
-  auto do_piece = [&](const int row, const int s0, const int s1, const int npieces, const int pi, long long *clk) {
+  auto do_piece = [&](const int row, const int s0, const int s1, const int npieces, const int pi, long long *clk_arg) {
+    long long *const clk = TIMED ? clk_arg : nullptr;  // phase stamps only exist in the timed instantiation
 #define QPB_STAMP(k) do { if (clk) clk[k] = clock64(); } while (0)
     QPB_STAMP(0);
     long long select_clk = 0;
@@ -73,9 +74,15 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, g0 + j);
 
     // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
-    MtFetch rng = {};
-    if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw)
-      rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+    // (the RNG words are only pulled towards L2 here: holding them in registers through the scan costs occupancy)
+    if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw) {
+      const unsigned int d = a.rng_drawn[row];
+      const unsigned long long *mt = a.rng_state + (size_t)row * MT_N;
+      const int k = (int)(d % MT_N);
+      prefetch_l2(mt + k);
+      prefetch_l2(mt + (k + 1 == MT_N ? 0 : k + 1));
+      prefetch_l2(mt + (k + MT_M >= MT_N ? k + MT_M - MT_N : k + MT_M));
+    }
     // history window (sampler.cpp:32-35): "hn > (size_t)repeat_last_n ? hn - repeat_last_n : 0", so a negative
     // repeat_last_n means the whole history
     const bool use_pen = p.repeat_penalty != 1.f && a.history != nullptr;
@@ -85,6 +92,11 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     const int *hrow = a.history + (size_t)row * a.hist_stride;
     int first_id = -1;
     if (use_pen && hfrom + tid < hn) first_id = hrow[hfrom + tid];
+    // a CTA that has the row to itself builds the penalty set while the first copies are in flight; otherwise the
+    // CTA that ends up finishing the row does it then
+    const bool early_pen = use_pen && csize == 1 && npieces == 1 && MODE == MODE_SAMPLE;
+    if (early_pen) pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
+    int npen = -1;
 
     const bool greedy = p.temperature <= 0.f;
     const int K = greedy ? 1 : (p.top_k > 0 ? min(p.top_k, Vt) : Vt);  // sampler.cpp:39-40
@@ -116,10 +128,11 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
           }
         }
       }
-      __syncthreads();  // the sample has been read by every thread
+      __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
       g0 += kStages;    // start the stream proper while the threshold is worked out (its tiles are fetched again)
       if (tid == 0)
         for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+      if (early_pen) npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
       // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
       const long long sample = (long long)kStages * kTile;
       long long r = (9LL * Mloc * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
@@ -417,11 +430,13 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     }
 
     // ---- this CTA finishes the row: exact budget from the distinct window ids (sampler.cpp:32-41) ----
-    int npen = 0;
-    if (use_pen) {
-      pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
-      __syncthreads();
-      npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
+    if (npen < 0) {
+      npen = 0;
+      if (use_pen) {
+        if (!early_pen) pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
+        __syncthreads();
+        npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
+      }
     }
     int M = min(Vt, K + npen);
     if (M >= Vt / 4) M = Vt;  // top_m returns the whole row in this case (sampler.cpp:14)
@@ -433,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     unsigned long long *sorted = reinterpret_cast<unsigned long long *>(&S.ring[0][0]);
     float *ev = reinterpret_cast<float *>(&S.cand[0]);
     float *pv = ev + kCandCap;
-    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, rng, clk);
+    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, clk);
     QPB_STAMP(7);
     __syncthreads();  // the ring (sorted) and the list are free for the next piece
     if (tid == 0) S.cand_count = 0;

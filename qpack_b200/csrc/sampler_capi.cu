@@ -35,7 +35,7 @@ struct qpb_sampler {
   long long routed_hist_cap = -1;
   int cluster = 0;
   int stream_slots = 0;  // CTAs of the streaming kernel resident on the GPU at once (0: not queried yet)
-  bool attr_done[4] = {false, false, false, false};
+  bool attr_done[6] = {false, false, false, false, false, false};
   int64_t launches = 0;
   // staging for the host-buffer entry point
   float *d_stage_logits = nullptr;
@@ -44,6 +44,9 @@ struct qpb_sampler {
   size_t stage_hist_bytes = 0;
   int *d_stage_hlen = nullptr;
   int *d_stage_ids = nullptr;
+  unsigned char *d_stage_dist = nullptr;
+  size_t stage_dist_bytes = 0;
+  double *d_uniform = nullptr;
   cudaStream_t own_stream = nullptr;
   long long *d_phase_clk = nullptr;  // [max_rows][16] when phase stamps are enabled
   // scratch of the persistent-piece schedule: winners of row pieces, their counts, pieces delivered per row
@@ -202,7 +205,15 @@ int launch_stream(qpb_sampler *s, const StreamArgs &args, int rows, int cluster,
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<MODE>, args));
+  if (MODE == MODE_SAMPLE && args.phase_clk) {
+    if (!s->attr_done[2 + MODE_MERGE]) {
+      QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<MODE_SAMPLE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      s->attr_done[2 + MODE_MERGE] = true;
+    }
+    QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<MODE_SAMPLE, true>, args));
+  } else {
+    QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<MODE>, args));
+  }
   s->launches++;
   return QPB_OK;
 }
@@ -381,6 +392,8 @@ int qpb_sampler_destroy(qpb_sampler *s) {
   cudaFree(s->d_stage_hist);
   cudaFree(s->d_stage_hlen);
   cudaFree(s->d_stage_ids);
+  cudaFree(s->d_stage_dist);
+  cudaFree(s->d_uniform);
   cudaFree(s->d_phase_clk);
   cudaFree(s->d_piece_cand);
   cudaFree(s->d_piece_cnt);
@@ -448,13 +461,14 @@ int qpb_sampler_check(qpb_sampler *s, void *stream) {
   return fail(s, QPB_ERR_INTERNAL, buf);
 }
 
-int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
-                            const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len,
-                            int hist_len_all, int32_t *h_out_ids) {
-  if (!s) return QPB_ERR_INVALID;
-  if (!h_logits || !h_out_ids) return fail(s, QPB_ERR_INVALID, "host pointer is null");
-  if (n_rows <= 0 || n_rows > s->max_rows || vocab <= 0 || row_stride < vocab)
+// host buffers in, host buffers out: staging on the handle's own stream
+static int host_call(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
+                     const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len, int hist_len_all,
+                     int32_t *h_dist_ids, float *h_dist_p, int32_t *h_dist_count, int max_out, int32_t *h_out_ids) {
+  if (!h_logits || (!h_out_ids && !h_dist_count)) return fail(s, QPB_ERR_INVALID, "host pointer is null");
+  if (n_rows <= 0 || n_rows > s->max_rows || vocab <= 0 || row_stride < vocab || max_out < 0)
     return fail(s, QPB_ERR_INVALID, "n_rows / vocab / row_stride out of range");
+  if (h_dist_count && max_out > 0 && (!h_dist_ids || !h_dist_p)) return fail(s, QPB_ERR_INVALID, "distribution output pointers are null");
   DeviceGuard g(s->device);
   cudaStream_t st = s->own_stream;
   const size_t lbytes = ((size_t)(n_rows - 1) * row_stride + vocab) * sizeof(float);
@@ -466,8 +480,17 @@ int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64_t row_s
     s->stage_logits_bytes = lbytes;
   }
   if (!s->d_stage_ids) {
-    QPB_CUDA(s, cudaMalloc(&s->d_stage_ids, sizeof(int) * s->max_rows));
+    QPB_CUDA(s, cudaMalloc(&s->d_stage_ids, sizeof(int) * 2 * s->max_rows));  // ids, then counts
     QPB_CUDA(s, cudaMalloc(&s->d_stage_hlen, sizeof(int) * s->max_rows));
+  }
+  const bool want_dist = h_dist_count != nullptr;
+  const size_t dbytes = want_dist ? (size_t)n_rows * max_out * 8 : 0;
+  if (dbytes > s->stage_dist_bytes) {
+    cudaFree(s->d_stage_dist);
+    s->d_stage_dist = nullptr;
+    s->stage_dist_bytes = 0;
+    QPB_CUDA(s, cudaMalloc(&s->d_stage_dist, dbytes));
+    s->stage_dist_bytes = dbytes;
   }
   const int *d_hist = nullptr, *d_hlen = nullptr;
   if (h_history && hist_stride > 0) {
@@ -488,10 +511,58 @@ int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64_t row_s
   }
   QPB_CUDA(s, cudaMemcpyAsync(s->d_stage_logits, h_logits, lbytes, cudaMemcpyHostToDevice, st));
   Inputs in{s->d_stage_logits, row_stride, n_rows, vocab, vocab, 0, d_hist, hist_stride, d_hlen, hist_len_all};
-  int rc = run_rows(s, in, nullptr, nullptr, nullptr, 0, s->d_stage_ids, true, st);
+  int32_t *d_ids = h_out_ids ? s->d_stage_ids : nullptr;
+  int32_t *d_cnt = want_dist ? s->d_stage_ids + s->max_rows : nullptr;
+  int32_t *d_dids = (want_dist && max_out > 0) ? reinterpret_cast<int32_t *>(s->d_stage_dist) : nullptr;
+  float *d_dp = (want_dist && max_out > 0) ? reinterpret_cast<float *>(s->d_stage_dist) + (size_t)n_rows * max_out : nullptr;
+  int rc = run_rows(s, in, d_dids, d_dp, d_cnt, max_out, d_ids, h_out_ids != nullptr, st);
   if (rc) return rc;
-  QPB_CUDA(s, cudaMemcpyAsync(h_out_ids, s->d_stage_ids, sizeof(int) * n_rows, cudaMemcpyDeviceToHost, st));
+  if (h_out_ids) QPB_CUDA(s, cudaMemcpyAsync(h_out_ids, d_ids, sizeof(int) * n_rows, cudaMemcpyDeviceToHost, st));
+  if (want_dist) {
+    QPB_CUDA(s, cudaMemcpyAsync(h_dist_count, d_cnt, sizeof(int) * n_rows, cudaMemcpyDeviceToHost, st));
+    if (max_out > 0) {
+      QPB_CUDA(s, cudaMemcpyAsync(h_dist_ids, d_dids, sizeof(int) * (size_t)n_rows * max_out, cudaMemcpyDeviceToHost, st));
+      QPB_CUDA(s, cudaMemcpyAsync(h_dist_p, d_dp, sizeof(float) * (size_t)n_rows * max_out, cudaMemcpyDeviceToHost, st));
+    }
+  }
   return qpb_sampler_check(s, st);
+}
+
+int qpb_sampler_sample_host(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
+                            const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len,
+                            int hist_len_all, int32_t *h_out_ids) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!h_out_ids) return fail(s, QPB_ERR_INVALID, "host pointer is null");
+  return host_call(s, h_logits, row_stride, n_rows, vocab, h_history, hist_stride, h_hist_len, hist_len_all, nullptr,
+                   nullptr, nullptr, 0, h_out_ids);
+}
+
+int qpb_sampler_dist_host(qpb_sampler *s, const float *h_logits, int64_t row_stride, int n_rows, int vocab,
+                          const int32_t *h_history, int64_t hist_stride, const int32_t *h_hist_len, int hist_len_all,
+                          int32_t *h_dist_ids, float *h_dist_p, int32_t *h_dist_count, int max_out,
+                          int32_t *h_out_ids) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!h_dist_count) return fail(s, QPB_ERR_INVALID, "host pointer is null");
+  return host_call(s, h_logits, row_stride, n_rows, vocab, h_history, hist_stride, h_hist_len, hist_len_all,
+                   h_dist_ids, h_dist_p, h_dist_count, max_out, h_out_ids);
+}
+
+// The next uniform variate of row's stream, as std::uniform_real_distribution<double>(0,1)(rng_) would return
+// it (src/sampler.cpp:60,68); advances the stream by one word.  For Sampler::draw / accept on host-side pairs.
+__global__ void next_uniform_kernel(unsigned long long *mt, unsigned int *drawn, double *out) {
+  *out = word_to_uniform(mt_next(mt, drawn));
+}
+int qpb_sampler_next_uniform(qpb_sampler *s, int row, double *h_u) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!h_u || row < 0 || row >= s->max_rows) return fail(s, QPB_ERR_INVALID, "row out of range");
+  DeviceGuard g(s->device);
+  if (!s->d_uniform) QPB_CUDA(s, cudaMalloc(&s->d_uniform, sizeof(double)));
+  next_uniform_kernel<<<1, 1, 0, s->own_stream>>>(s->d_rng + (size_t)row * MT_N, s->d_drawn + row, s->d_uniform);
+  QPB_CUDA(s, cudaGetLastError());
+  s->launches++;
+  QPB_CUDA(s, cudaMemcpyAsync(h_u, s->d_uniform, sizeof(double), cudaMemcpyDeviceToHost, s->own_stream));
+  QPB_CUDA(s, cudaStreamSynchronize(s->own_stream));
+  return QPB_OK;
 }
 
 int qpb_sampler_rng_get(qpb_sampler *s, int row, uint64_t *h_state313) {

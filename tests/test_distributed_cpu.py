@@ -1,0 +1,102 @@
+"""CPU tests (gloo, world size 2) of the multi-GPU host logic: the row partition and the vocabulary-sharded flow
+(local candidates -> all-gather -> merge).  The GPU kernels are replaced by a NumPy stand-in that produces the same
+64-bit (key, ~global id) candidate entries, and the merge is decoded and finished by the CPU checker, so the test
+checks the partition arithmetic, the gather layout and that exact local winners suffice for the global result."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import Oracle
+from qpack_b200 import synth
+from qpack_b200.distributed import gather_candidates, row_partition, sample_vocab_sharded, vocab_shard
+
+
+def f2key(x):
+    b = x.astype(np.float32).view(np.uint32).astype(np.uint64)
+    b = np.where(b == 0x80000000, 0, b)
+    return np.where(b & 0x80000000, (~b) & 0xFFFFFFFF, b | 0x80000000).astype(np.uint64)
+
+
+class NumpySampler:
+    """Stand-in with the BatchSampler calls the sharded flow uses."""
+
+    def __init__(self, params, logits_full):
+        self.params, self.full = params, logits_full
+
+    def cand_slots(self, vocab_total, per_max):
+        return int(min(per_max, self.params["top_k"].max()))
+
+    def local_candidates(self, shard, vocab_total, id_offset, slots, history=None, hist_len=None):
+        x = shard.numpy()
+        out = np.zeros((x.shape[0], slots), np.uint64)
+        for r in range(x.shape[0]):
+            comp = (f2key(x[r]) << np.uint64(32)) | (np.uint64(0xFFFFFFFF) - (np.arange(x.shape[1], dtype=np.uint64) + np.uint64(id_offset)))
+            top = np.sort(comp)[::-1][:slots]
+            out[r, :len(top)] = top
+        return torch.from_numpy(out.view(np.int64))
+
+    def merge_sample(self, allc, vocab_total, history=None, hist_len=None, max_out=0):
+        c = allc.numpy().view(np.uint64)
+        G, B, S = c.shape
+        ids = np.empty(B, np.int32)
+        for r in range(B):
+            ent = c[:, r, :].reshape(-1)
+            ent = ent[ent != 0]
+            # rebuild a row that holds only the gathered columns (everything else far below) and let the checker finish
+            row = np.full(vocab_total, -np.inf, np.float32)
+            gid = (np.uint64(0xFFFFFFFF) - (ent & np.uint64(0xFFFFFFFF))).astype(np.int64)
+            row[gid] = self.full[r, gid]
+            ids[r] = Oracle(self.params[r:r + 1]).sample(row)
+        return torch.from_numpy(ids)
+
+
+def _worker(rank, world, port, rows, vocab):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    wl = synth.sharded_batch(rows=rows, vocab=vocab)
+    b, e = vocab_shard(vocab, world, rank)
+    shard = torch.from_numpy(np.ascontiguousarray(wl.logits[:, b:e]))
+    ids = sample_vocab_sharded(NumpySampler(wl.params, wl.logits), shard, vocab, b)
+    want = Oracle.sample_rows(wl.params, wl.logits)["ids"]
+    assert np.array_equal(ids.numpy(), want), (rank, ids.numpy(), want)
+    # the gather puts rank g's entries at [g]
+    t = torch.full((3, 2), rank, dtype=torch.int64)
+    g = gather_candidates(t)
+    assert g.shape == (world, 3, 2) and all(int(g[k, 0, 0]) == k for k in range(world))
+    # rows: each rank samples its own block, no collective; together they cover every row once
+    rb, re_ = row_partition(rows, world, rank)
+    mine = Oracle.sample_rows(wl.params[rb:re_], wl.logits[rb:re_])["ids"]
+    assert np.array_equal(mine, want[rb:re_])
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_partitions_cover_everything_once():
+    for n, w in ((1024, 8), (1000, 3), (5, 8), (128, 2)):
+        spans = [row_partition(n, w, r) for r in range(w)]
+        assert spans[0][0] == 0 and spans[-1][1] == n
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(w - 1))
+        assert max(e - b for b, e in spans) - min(e - b for b, e in spans) <= 1
+    for v, w in ((151936, 8), (151936, 2), (1001, 4), (7, 8)):
+        spans = [vocab_shard(v, w, r) for r in range(w)]
+        assert spans[0][0] == 0 and spans[-1][1] == v
+        assert all(spans[i][1] == spans[i + 1][0] for i in range(w - 1))
+        assert all(b % 4 == 0 for b, e in spans if e > b)
+    assert vocab_shard(151936, 8, 1) == (18992, 37984)  # 18992 ids per GPU at 8
+
+
+def test_vocab_sharded_flow_world_size_2():
+    mp.spawn(_worker, args=(2, _free_port(), 6, 4096), nprocs=2, join=True)

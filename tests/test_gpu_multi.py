@@ -1,0 +1,58 @@
+"""Two-GPU tests (NCCL): vocabulary-sharded sampling with a real all-gather, and row partition.  Skipped when
+fewer than two GPUs are visible."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import Oracle
+from qpack_b200 import synth
+from qpack_b200.distributed import row_partition, sample_vocab_sharded, vocab_shard
+from qpack_b200.sampler import BatchSampler
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dev = f"cuda:{rank}"
+    # vocabulary shards (config 5): ids equal the checker on the whole row
+    wl = synth.sharded_batch(rows=32)
+    V = wl.vocab
+    b, e = vocab_shard(V, world, rank)
+    shard = torch.from_numpy(np.ascontiguousarray(wl.logits[:, b:e])).to(dev)
+    bs = BatchSampler(wl.rows, rank)
+    bs.set_params(wl.params)
+    ids = sample_vocab_sharded(bs, shard, V, b)
+    bs.check()
+    want = Oracle.sample_rows(wl.params, wl.logits)["ids"]
+    assert np.array_equal(ids.cpu().numpy(), want), rank
+    bs.close()
+    # rows (config 4): each rank its block, no collective on the data path
+    wl = synth.serving_batch(rows=64)
+    rb, re_ = row_partition(wl.rows, world, rank)
+    bs = BatchSampler(re_ - rb, rank)
+    bs.set_params(wl.params[rb:re_])
+    out = bs.sample(torch.from_numpy(wl.logits[rb:re_]).to(dev), torch.from_numpy(wl.history[rb:re_]).to(dev))
+    bs.check()
+    want = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len)["ids"]
+    assert np.array_equal(out.cpu().numpy(), want[rb:re_]), rank
+    bs.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_sharded_and_row_partition():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_worker, args=(2, port), nprocs=2, join=True)
