@@ -240,25 +240,27 @@ __device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int 
 // cand[0..n): a superset of the candidates the reference would hold, unordered (exactly its M largest raw
 // entries when the caller had to cut to M).  `sorted` (kCandCap composites) must not overlap cand; ev / pv
 // (kCandCap floats each) may alias cand, which is dead once `sorted` is written.
+// candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied.  All threads call it.
+__device__ __forceinline__ void penalise_candidates(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
+                                                    const uint32_t *bloom, float rp) {
+  for (int i = threadIdx.x; i < n; i += kThreads) {
+    const unsigned long long c = cand[i];
+    const int id = comp_id(c);
+    const uint32_t b = pen_bloom_bit(id);
+    if (((bloom[b >> 5] >> (b & 31)) & 1u) && pen_contains(pen_tab, pen_slots, id)) {
+      float v = key2f(comp_key(c));
+      v = v > 0.f ? __fdiv_rn(v, rp) : __fmul_rn(v, rp);
+      cand[i] = make_comp(f2key(v), (uint32_t)id);
+    }
+  }
+  __syncthreads();
+}
+
 __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
                            const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv,
-                           StreamSmem &S, long long *clk) {
+                           StreamSmem &S, long long *clk, bool penalised = false) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied
-  if (npen > 0) {
-    const float rp = p.repeat_penalty;
-    for (int i = threadIdx.x; i < n; i += kThreads) {
-      const unsigned long long c = cand[i];
-      const int id = comp_id(c);
-      const uint32_t b = pen_bloom_bit(id);
-      if (((S.pen_bloom[b >> 5] >> (b & 31)) & 1u) && pen_contains(pen_tab, a.pen_slots, id)) {
-        float v = key2f(comp_key(c));
-        v = v > 0.f ? __fdiv_rn(v, rp) : __fmul_rn(v, rp);
-        cand[i] = make_comp(f2key(v), (uint32_t)id);
-      }
-    }
-    __syncthreads();
-  }
+  if (npen > 0 && !penalised) penalise_candidates(cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
   if (clk) clk[11] = clock64();
   // the K best by (value desc, id asc) (sampler.cpp:43-44): select, then rank = number of larger composites
   n = block_keep_top(cand, n, K, S.hist, S.sel, &S.cand_count);

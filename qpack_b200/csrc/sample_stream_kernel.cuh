@@ -105,6 +105,12 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     int Mloc = (int)min((long long)Vt, (long long)K + wlen);
     if (Mloc >= Vt / 4) Mloc = Vt;
     const int need = min(Mloc, s1 - s0);  // columns this piece must deliver
+    // A CTA that finishes its row alone, with a penalty that only lowers values (or none), can aim lower: the K
+    // best after the penalty all have a RAW value above any threshold that at least K penalised values exceed
+    // (penalised <= raw), so it is enough to collect the columns above a threshold aimed at K + a margin and to
+    // check afterwards that K of them still exceed it once penalised.
+    const bool lean = csize == 1 && npieces == 1 && MODE == MODE_SAMPLE && (!use_pen || p.repeat_penalty >= 1.f);
+    bool shrunk = false, penalised = false;
 
     // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
     // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
@@ -135,8 +141,9 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       if (early_pen) npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
       // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
       const long long sample = (long long)kStages * kTile;
-      long long r = (9LL * Mloc * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
-      r = r < 16 ? 16 : r;
+      const long long aim = lean ? min((long long)Mloc, (long long)K + 16 + K / 4) : (long long)Mloc;
+      long long r = (9LL * aim * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
+      r = r < (lean ? 12 : 16) ? (lean ? 12 : 16) : r;
       booted = Mloc < Vt && r <= 200;  // two maxima per thread hold the sample's best couple of hundred well enough
       if (booted) {
         S.cand[2 * tid] = make_comp(f2key(m1), (uint32_t)(2 * tid));
@@ -151,6 +158,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
 
     // keep the Mloc best of the list and raise the threshold to the weakest of them; all threads call it
     auto shrink = [&]() {
+      shrunk = true;
       const long long c0 = clk ? clock64() : 0;
       block_keep_top(S.cand, min(S.cand_count, kCandCap), Mloc, S.hist, S.sel, &S.cand_count);
       // later columns must beat the weakest kept key: an equal key at a higher index loses.  The select may stop
@@ -323,7 +331,20 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       g0 += n_tiles;  // every slot up to here has been issued and consumed
       // every column above the bootstrap threshold was collected; with at least `need` of them the needed ones
       // are all in the list.  Otherwise the guess was too high: stream the piece once more from "no threshold".
-      if (!booted || S.cand_count >= need) break;
+      if (!booted) break;
+      if (lean && !shrunk) {
+        // every column with a raw value above thr is in the list; K of them still above it after the penalty?
+        const int nl = min(S.cand_count, kCandCap);
+        if (npen < 0) npen = 0;  // (with a penalty the set was built during the bootstrap)
+        if (npen > 0) penalise_candidates(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
+        const uint32_t tkey = f2key(thr);
+        int above = 0;
+        for (int i0 = 0; i0 < nl; i0 += kThreads)
+          above += __syncthreads_count(i0 + tid < nl && comp_key(S.cand[i0 + tid]) > tkey);
+        if (above >= min(K, s1 - s0)) { penalised = true; break; }
+      } else if (S.cand_count >= need) {
+        break;
+      }
       __syncthreads();
       booted = false;
       thr = __int_as_float(0x7fc00000);
@@ -448,7 +469,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     unsigned long long *sorted = reinterpret_cast<unsigned long long *>(&S.ring[0][0]);
     float *ev = reinterpret_cast<float *>(&S.cand[0]);
     float *pv = ev + kCandCap;
-    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, clk);
+    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, clk, penalised);
     QPB_STAMP(7);
     __syncthreads();  // the ring (sorted) and the list are free for the next piece
     if (tid == 0) S.cand_count = 0;
