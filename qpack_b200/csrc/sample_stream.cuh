@@ -260,6 +260,9 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
                            const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv,
                            StreamSmem &S, long long *clk, bool penalised = false) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the RNG words of a possible draw: requested now, used after the ordering and the softmax
+  MtFetch rng = {};
+  if (threadIdx.x == 0 && a.draw && p.temperature > 0.f) rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
   if (npen > 0 && !penalised) penalise_candidates(cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
   if (clk) clk[11] = clock64();
   // the K best by (value desc, id asc) (sampler.cpp:43-44): select, then rank = number of larger composites
@@ -309,35 +312,49 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   double sum = 0.0;
 #pragma unroll 8
   for (int j = 0; j < nK; ++j) sum += (double)ev[j];
+  if (clk) clk[13] = clock64();
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
   const bool use_minp = p.min_p > 0.f;
   const double top_p = (double)p.top_p;
   int keep = nK;
   double cum = 0.0;
   bool done = false;
-  for (int base = 0; base < nK && !done; base += 32) {  // sampler.cpp:48-52
+  double *qs = reinterpret_cast<double *>(S.hist);  // 32 quotients of the current chunk (the histogram is idle)
+  for (int base = 0; base < nK && !done; base += 32) {  // sampler.cpp:48-52, 32 positions at a time
     const int i = base + lane;
     const float e = i < nK ? ev[i] : 0.f;
-    const double q = __ddiv_rn((double)e, sum);
+    qs[lane] = __ddiv_rn((double)e, sum);
     const bool fail = use_minp && i < nK && e < minp_thr;
     const uint32_t failmask = __ballot_sync(0xffffffffu, fail);
     const int cnt = nK - base < 32 ? nK - base : 32;
-    for (int j = 0; j < cnt; ++j) {
-      if ((failmask >> j) & 1u) { keep = base + j > 1 ? base + j : 1; done = true; break; }
-      cum += __shfl_sync(0xffffffffu, q, j);
-      if (cum >= top_p) { keep = base + j + 1; done = true; break; }
+    __syncwarp();
+    // the running sum is a dependent chain of double adds; without branches inside, its loads and compares overlap
+    int first_top = 32;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const double next = cum + qs[j];
+      const bool valid = j < cnt;
+      cum = valid ? next : cum;
+      first_top = (valid && first_top == 32 && next >= top_p) ? j : first_top;
     }
+    const int first_fail = failmask ? __ffs(failmask) - 1 : 32;
+    // position i: the min-p test comes first, then the sum test (sampler.cpp:50-51)
+    if (first_fail <= first_top && first_fail < 32) { keep = base + first_fail > 1 ? base + first_fail : 1; done = true; }
+    else if (first_top < 32) { keep = base + first_top + 1; done = true; }
+    __syncwarp();
   }
+  if (clk) clk[15] = clock64();
   double tot = 0.0;
 #pragma unroll 8
   for (int j = 0; j < keep; ++j) tot += (double)ev[j];  // sampler.cpp:54
   for (int j = lane; j < keep; j += 32) pv[j] = __double2float_rn(__ddiv_rn((double)ev[j], tot));  // :55
   __syncwarp();
+  if (clk) clk[3] = clock64();
   // draw (sampler.cpp:58-63)
   int pick = 0;
   if (keep > 1 && a.draw) {
     unsigned long long w = 0;
-    if (lane == 0) w = mt_next(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
+    if (lane == 0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
     w = __shfl_sync(0xffffffffu, w, 0);
     double r = word_to_uniform(w);
     pick = keep - 1;

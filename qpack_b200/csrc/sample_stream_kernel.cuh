@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     if (use_pen && hfrom + tid < hn) first_id = hrow[hfrom + tid];
     // a CTA that has the row to itself builds the penalty set while the first copies are in flight; otherwise the
     // CTA that ends up finishing the row does it then
-    const bool early_pen = use_pen && csize == 1 && npieces == 1 && MODE == MODE_SAMPLE;
+    const bool early_pen = use_pen && crank == 0 && npieces == 1 && MODE == MODE_SAMPLE;
     if (early_pen) pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
     int npen = -1;
 
@@ -109,8 +109,9 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // best after the penalty all have a RAW value above any threshold that at least K penalised values exceed
     // (penalised <= raw), so it is enough to collect the columns above a threshold aimed at K + a margin and to
     // check afterwards that K of them still exceed it once penalised.
-    const bool lean = csize == 1 && npieces == 1 && MODE == MODE_SAMPLE && (!use_pen || p.repeat_penalty >= 1.f);
+    const bool lean = npieces == 1 && MODE == MODE_SAMPLE && (!use_pen || p.repeat_penalty >= 1.f);
     bool shrunk = false, penalised = false;
+    int n = 0;  // entries of the list once it is final
 
     // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
     // weakest kept value, and an equal value at a higher index loses (strict compare, sampler.cpp:16 and
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // Fast mode scans a whole tile between two barriers and expects a handful of survivors.  Careful mode (no
     // threshold yet, or a tile that overflowed the list in fast mode) scans a chunk of a tile at a time and
     // selects whenever another chunk might not fit, so the list can never overflow whatever the data.
-    for (int attempt = 0; attempt < 2; ++attempt) {
+    for (int attempt = 0; attempt < 3; ++attempt) {
       bool careful = false;
       for (int t = 0; t < n_tiles;) {
         const int g = g0 + t;
@@ -329,22 +330,86 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
         ++t;
       }
       g0 += n_tiles;  // every slot up to here has been issued and consumed
-      // every column above the bootstrap threshold was collected; with at least `need` of them the needed ones
-      // are all in the list.  Otherwise the guess was too high: stream the piece once more from "no threshold".
-      if (!booted) break;
-      if (lean && !shrunk) {
-        // every column with a raw value above thr is in the list; K of them still above it after the penalty?
-        const int nl = min(S.cand_count, kCandCap);
-        if (npen < 0) npen = 0;  // (with a penalty the set was built during the bootstrap)
-        if (npen > 0) penalise_candidates(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
-        const uint32_t tkey = f2key(thr);
+      // Is the list good?  Without a bootstrap guess it holds the exact best Mloc by construction.  With one, every
+      // column above the threshold was collected: with at least `need` of them the needed ones are all in the
+      // list; a lean guess is judged after the penalty instead (by this CTA, or by the cluster leader on the
+      // merged list).  A bad guess means streaming once more from "no threshold".
+      auto build_pen_now = [&]() {
+        if (npen >= 0) return;
+        npen = 0;
+        if (use_pen) {
+          if (!early_pen) pen_clear(pen_tab, a.pen_slots, &S.pen_unique, S.pen_bloom);
+          __syncthreads();
+          npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
+        }
+      };
+      auto count_above = [&](int nl, uint32_t tkey) {  // entries of the list whose key exceeds tkey
         int above = 0;
         for (int i0 = 0; i0 < nl; i0 += kThreads)
           above += __syncthreads_count(i0 + tid < nl && comp_key(S.cand[i0 + tid]) > tkey);
-        if (above >= min(K, s1 - s0)) { penalised = true; break; }
-      } else if (S.cand_count >= need) {
-        break;
+        return above;
+      };
+      bool ok = true, guess = false;
+      if (booted) {
+        if (lean && !shrunk) {
+          if (csize == 1) {
+            const int nl = min(S.cand_count, kCandCap);
+            build_pen_now();
+            if (npen > 0) penalise_candidates(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
+            ok = count_above(nl, f2key(thr)) >= min(K, s1 - s0);
+            penalised = ok;
+          } else {
+            guess = true;  // the leader judges the merged list
+          }
+        } else {
+          ok = S.cand_count >= need;
+        }
       }
+      if (ok && csize > 1 && MODE == MODE_SAMPLE) {
+        // ---- cluster merge: every CTA pushes its list into the leader's over DSMEM ----
+        n = min(S.cand_count, kCandCap);
+        if (n > Mloc) { n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count); guess = false; }
+        StreamSmem *L = cluster.map_shared_rank(&S, 0);
+        if (crank == 0 && tid == 0) { S.sel[3] = guess ? f2key(thr) : 0u; S.misc[1] = 0; }
+        cluster.sync();  // the leader's ring is idle, its own list and its verdict words are set
+        if (crank != 0) {
+          if (tid == 0) {
+            S.misc[0] = atomicAdd(&L->cand_count, n);
+            if (guess) atomicMax(&L->sel[3], f2key(thr));
+          }
+          __syncthreads();
+          const int base = S.misc[0];
+          for (int i = tid; i < n; i += kThreads)
+            if (base + i < kMergeCap) L->cand[base + i] = S.cand[i];
+          if (base + n > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
+        }
+        cluster.sync();  // every list has arrived
+        const uint32_t tmax = L->sel[3];  // highest guessed threshold in the cluster (0: nobody guessed)
+        bool redo = false;
+        if (tmax != 0u) {
+          if (crank == 0) {
+            // lists of guessing CTAs hold every column above their threshold, the others their exact best Mloc:
+            // the merged list is good if K entries still exceed the highest guess once penalised
+            n = min(S.cand_count, kMergeCap);
+            build_pen_now();
+            if (npen > 0) penalise_candidates(S.cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
+            penalised = true;
+            if (count_above(n, tmax) < min(K, Vt) && tid == 0) S.misc[1] = 1;
+          }
+          cluster.sync();  // the verdict is in
+          redo = L->misc[1] != 0;
+        }
+        if (!redo) {
+          if (crank != 0) return;
+          n = min(S.cand_count, kMergeCap);
+          n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
+          break;
+        }
+        ok = false;  // every CTA of the cluster streams its slice again, exactly
+        penalised = false;
+        cluster.sync();  // nobody resets anything before everybody has read the verdict
+      }
+      if (ok) break;
       __syncthreads();
       booted = false;
       thr = __int_as_float(0x7fc00000);
@@ -381,28 +446,15 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       if (S.cand_count > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
     }
 
-    int n = min(S.cand_count, MODE == MODE_MERGE ? kMergeCap : kCandCap);
-    // Lists that travel (cluster merge, piece scratch, all-gather) are cut to the streaming budget first.
-    const bool travels = csize > 1 || npieces > 1 || MODE != MODE_SAMPLE;
+    const bool merged = csize > 1 && MODE == MODE_SAMPLE;  // the leader already holds the merged, cut list
+    if (!merged) n = min(S.cand_count, MODE == MODE_MERGE ? kMergeCap : kCandCap);
+    // Lists that travel (piece scratch, all-gather) are cut to the streaming budget first.
+    const bool travels = !merged && (csize > 1 || npieces > 1 || MODE != MODE_SAMPLE);
     if (travels) n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
     QPB_STAMP(3);
 
-    if (csize > 1) {
-      // ---- cluster merge: every CTA pushes its winners into the leader's list over DSMEM ----
-      cluster.sync();  // the leader's ring is idle and its own list is final
-      if (crank != 0) {
-        StreamSmem *L = cluster.map_shared_rank(&S, 0);
-        if (tid == 0) S.misc[0] = atomicAdd(&L->cand_count, n);
-        __syncthreads();
-        const int base = S.misc[0];
-        for (int i = tid; i < n; i += kThreads)
-          if (base + i < kMergeCap) L->cand[base + i] = S.cand[i];
-        if (base + n > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
-      }
-      cluster.sync();
-      if (crank != 0) return;
-      n = min(S.cand_count, kMergeCap);
-      n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
+    if (merged) {
+      // (merge done inside the loop above)
     } else if (npieces > 1) {
       // ---- row in pieces: leave this piece's winners in scratch; whoever delivers the last piece finishes ----
       const int slot_row = a.units_per_cta > 0 ? row : 0;  // scratch is indexed by row
