@@ -105,6 +105,7 @@ static_assert(kPenBloomBits == 1 << 12, "pen_bloom_bit takes 12 hash bits");
 
 __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) {
   uint32_t h = pen_hash(id, slots);
+#pragma unroll 1
   for (int probe = 0; probe < slots; ++probe) {
     const int t = tab[h];
     if (t == id) return true;
@@ -126,6 +127,7 @@ __device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_
   if (t < 0 || t >= vocab_total) return 0;  // out-of-range ids are skipped (sampler.cpp:36)
   if (bloom) { const uint32_t b = pen_bloom_bit(t); atomicOr(&bloom[b >> 5], 1u << (b & 31)); }
   uint32_t h = pen_hash(t, slots);
+#pragma unroll 1
   for (int probe = 0; probe < slots; ++probe) {
     const int old = atomicCAS(&tab[h], kPenEmpty, t);
     if (old == kPenEmpty) return 1;
@@ -146,6 +148,8 @@ __device__ int pen_build(int *tab, int slots, int *unique_ctr, const int *hist, 
   return *unique_ctr;
 }
 
+// (The block-wide helpers below are called from many places and kept out of line: the cold phases of the kernel are
+// limited by instruction fetch, so code size matters more than call overhead.)
 // ---- radix select over composites ------------------------------------------------------------------------
 // Returns a pivot such that exactly `want` of c[0..n) are >= pivot (composites are distinct).  0 < want < n.
 // 8-bit digits from the top; stops as soon as the chosen bucket is taken whole.  All threads call it.
@@ -157,7 +161,7 @@ __device__ unsigned long long block_select_pivot(const unsigned long long *c, in
   hist[threadIdx.x] = 0;  // kThreads == 256
   __syncthreads();
   for (int shift = 56; shift >= 0; shift -= 8) {
-#pragma unroll 4
+#pragma unroll 1
     for (int i = threadIdx.x; i < n; i += kThreads) {
       const unsigned long long v = c[i];
       if ((v & mask) == prefix) atomicAdd(&hist[(uint32_t)(v >> shift) & 255u], 1u);
@@ -199,6 +203,7 @@ __device__ int block_compact(unsigned long long *c, int n, unsigned long long pi
   const int lane = threadIdx.x & 31;
   if (threadIdx.x == 0) *counter = 0;
   __syncthreads();
+#pragma unroll 1
   for (int base = 0; base < n; base += PER * kThreads) {
     unsigned long long r[PER];
     int mine = 0;
@@ -243,6 +248,7 @@ __device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int 
 // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied.  All threads call it.
 __device__ __forceinline__ void penalise_candidates(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
                                                     const uint32_t *bloom, float rp) {
+#pragma unroll 1
   for (int i = threadIdx.x; i < n; i += kThreads) {
     const unsigned long long c = cand[i];
     const int id = comp_id(c);
@@ -279,7 +285,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
       const int i = i0 + threadIdx.x / P;
       const unsigned long long c = i < nK ? cand[i] : 0ULL;
       int rank = 0;
-#pragma unroll 4
+#pragma unroll 2
       for (int j = sub; j < nK; j += P) rank += (cand[j] > c) ? 1 : 0;
       for (int o = P >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
       if (i < nK && sub == 0) sorted[rank] = c;
@@ -310,7 +316,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
 
   // Ordered double arithmetic, replayed exactly: every lane of warp 0 carries the same running values.
   double sum = 0.0;
-#pragma unroll 8
+#pragma unroll 4
   for (int j = 0; j < nK; ++j) sum += (double)ev[j];
   if (clk) clk[13] = clock64();
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
@@ -330,7 +336,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     __syncwarp();
     // the running sum is a dependent chain of double adds; without branches inside, its loads and compares overlap
     int first_top = 32;
-#pragma unroll
+#pragma unroll 8
     for (int j = 0; j < 32; ++j) {
       const double next = cum + qs[j];
       const bool valid = j < cnt;
@@ -345,7 +351,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   }
   if (clk) clk[15] = clock64();
   double tot = 0.0;
-#pragma unroll 8
+#pragma unroll 4
   for (int j = 0; j < keep; ++j) tot += (double)ev[j];  // sampler.cpp:54
   for (int j = lane; j < keep; j += 32) pv[j] = __double2float_rn(__ddiv_rn((double)ev[j], tot));  // :55
   __syncwarp();
@@ -358,6 +364,7 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     w = __shfl_sync(0xffffffffu, w, 0);
     double r = word_to_uniform(w);
     pick = keep - 1;
+#pragma unroll 1
     for (int j = 0; j < keep; ++j) {
       r -= (double)pv[j];
       if (r <= 0.0) { pick = j; break; }

@@ -165,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       // later columns must beat the weakest kept key: an equal key at a higher index loses.  The select may stop
       // on a key prefix, so take the minimum over the kept entries.
       uint32_t mk = 0xffffffffu;
+#pragma unroll 1
       for (int i = tid; i < Mloc; i += kThreads) mk = min(mk, comp_key(S.cand[i]));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mk = min(mk, __shfl_xor_sync(0xffffffffu, mk, o));
@@ -252,12 +253,14 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
         if (tile_bulk(t)) {
           if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g / kStages) & 1u)) failed = true;
         } else {  // unaligned row or ragged tail: plain loads into the same stage
+#pragma unroll 1
           for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
           if (tid == 0) mbar_arrive(&S.full[st]);  // nobody waits on it, but the slot's phase has to advance
           __syncthreads();
         }
         const int cnt_before = S.cand_count;  // settled: the previous tile ended with a barrier
         const bool slow = careful || thr != thr;
+#pragma unroll 1
         for (int q = 0; q < kTile / kChunk; ++q) {
           const int qlen = min(kChunk, len - q * kChunk);  // columns of this chunk (uniform)
           if (qlen <= 0) break;
@@ -529,30 +532,37 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
 #undef QPB_STAMP
   };  // do_piece
 
-  if (a.units_per_cta > 0) {
-    // persistent pieces: CTA b owns the tiles [b * Q, (b + 1) * Q) of the rows laid end to end
-    const long long Q = a.units_per_cta, tpr = a.tiles_per_row;
-    const long long total = (long long)a.n_rows * tpr;
-    const long long u0 = (long long)blockIdx.x * Q, u1 = min(total, u0 + Q);
-    for (long long u = u0; u < u1;) {
-      const long long r = u / tpr;
+  // One call site for do_piece (it is large): both schedules are expressed as a run of tile units.
+  const bool pieces = a.units_per_cta > 0;
+  const long long Q = pieces ? a.units_per_cta : 1, tpr = pieces ? a.tiles_per_row : 1;
+  const long long total = (long long)a.n_rows * tpr;
+  long long u = pieces ? (long long)blockIdx.x * Q : (long long)(blockIdx.x / csize);
+  const long long u1 = pieces ? min(total, u + Q) : u + 1;
+  while (u < u1) {
+    const long long r = u / tpr;
+    const int row = a.row_list ? a.row_list[r] : (int)r;
+    int s0, s1, npieces = 1, pi = 0;
+    long long *clk = nullptr;
+    if (pieces) {
+      // persistent pieces: CTA b owns the tiles [b * Q, (b + 1) * Q) of the rows laid end to end
       const int t0 = (int)(u - r * tpr), t1 = (int)min(tpr, u1 - r * tpr);
       const long long first = (r * tpr) / Q, last = ((r + 1) * tpr - 1) / Q;
-      const int row = a.row_list ? a.row_list[r] : (int)r;
-      do_piece(row, min(a.vocab, t0 * kTile), min(a.vocab, t1 * kTile), (int)(last - first + 1),
-               (int)((long long)blockIdx.x - first), nullptr);
+      s0 = min(a.vocab, t0 * kTile);
+      s1 = min(a.vocab, t1 * kTile);
+      npieces = (int)(last - first + 1);
+      pi = (int)((long long)blockIdx.x - first);
       u = r * tpr + t1;
+    } else {
+      // one row per cluster: this CTA's slice, cut at multiples of 4 floats to keep 16-byte alignment
+      int per = (a.vocab + csize - 1) / csize;
+      per = (per + 3) & ~3;
+      s0 = min(a.vocab, crank * per);
+      s1 = min(a.vocab, s0 + per);
+      clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
+      if (TIMED && clk) { clk[11] = 0; clk[12] = 0; clk[13] = 0; clk[14] = 0; clk[15] = 0; }
+      u = u1;
     }
-  } else {
-    // one row per cluster: this CTA's slice, cut at multiples of 4 floats to keep 16-byte alignment
-    const int slot = blockIdx.x / csize;
-    const int row = a.row_list ? a.row_list[slot] : slot;
-    int per = (a.vocab + csize - 1) / csize;
-    per = (per + 3) & ~3;
-    const int s0 = min(a.vocab, crank * per), s1 = min(a.vocab, s0 + per);
-    long long *clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
-    if (clk) { clk[11] = 0; clk[12] = 0; clk[13] = 0; clk[14] = 0; clk[15] = 0; }
-    do_piece(row, s0, s1, 1, 0, clk);
+    do_piece(row, s0, s1, npieces, pi, clk);
   }
 }
 
