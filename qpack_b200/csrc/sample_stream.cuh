@@ -22,23 +22,38 @@
 namespace qpb {
 namespace cg = cooperative_groups;
 
-constexpr int kThreads = 256;                // threads per CTA
-constexpr int kTile = 4096;                  // floats per ring stage (16 KB)
-constexpr int kStages = 2;                   // ring depth: 32 KB in flight per CTA, 4 CTAs per SM
-constexpr int kChunk = kThreads * 4;         // careful mode scans a tile in chunks of one float4 per thread
-constexpr int kCandCap = 2048;               // candidate entries of the streaming phase (16 KB)
-constexpr int kCandHigh = kCandCap - kChunk; // careful mode: select when the list grows beyond this (a chunk adds <= kChunk)
-constexpr int kCandHighFast = 1280;          // fast mode: select after a tile that left more than this
+#ifndef QPB_STREAM_THREADS
+#define QPB_STREAM_THREADS 256
+#endif
+constexpr int kThreads = QPB_STREAM_THREADS;  // threads per CTA; the other sizes follow from it
+constexpr int kCtasPerSm = 1024 / kThreads;   // resident CTAs per SM the kernel is built for (64 registers a thread)
+constexpr int kTile = kThreads * 16;          // floats per ring stage: four float4 per thread
+constexpr int kStages = 2;                    // ring depth; kStages * kTile * 4 bytes in flight per CTA
+constexpr int kChunk = kThreads * 4;          // careful mode scans a tile in chunks of one float4 per thread
+constexpr int kCandCap = kThreads * 8;        // candidate entries of the streaming phase
+constexpr int kCandHigh = kCandCap - kChunk;  // careful mode: select when the list grows beyond this (a chunk adds <= kChunk)
+constexpr int kCandHighFast = kThreads * 5;   // fast mode: select after a tile that left more than this
 constexpr int kRingEntries = kStages * kTile * 4 / 8;
-constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to the cluster merge (ring reused)
-// Rows with top_k + window above this take the whole-row kernel instead.  It also bounds the "whole row" case of
-// top_m (M >= V/4 implies V <= 4 * 500 + 3 = 2003 <= kCandCap).
+constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to a merge (the ring is reused)
+// Rows with top_k + window above this take the whole-row kernel instead, and so do rows whose budget reaches a
+// quarter of the vocabulary (top_m then returns the whole row, sampler.cpp:14): the host routes them away.
 constexpr int kSmallMaxM = 500;
+constexpr int kMaxStreamCluster = kMergeCap / kSmallMaxM >= 8 ? 8 : 4;  // CTAs whose lists fit the leader's merge
+#ifndef QPB_BOOT_PREFETCH_TILES
+#define QPB_BOOT_PREFETCH_TILES 0
+#endif
+#ifndef QPB_LEAN_MIN_RANK
+#define QPB_LEAN_MIN_RANK 12
+#endif
+constexpr int kBootPrefetchTiles = QPB_BOOT_PREFETCH_TILES;  // tiles asked into L2 while the threshold is bootstrapped
+constexpr int kLeanMinRank = QPB_LEAN_MIN_RANK;              // lowest sample rank a lean threshold is taken at
 constexpr int kPenBloomBits = 4096;          // one-probe negative test in front of the penalty hash table
 constexpr int kPenEmpty = -1;
-static_assert(kSmallMaxM <= kCandHigh && 4 * kSmallMaxM + 3 <= kCandCap, "candidate list sizing");
-static_assert(8 * kSmallMaxM <= kMergeCap, "cluster merge sizing");
+static_assert(kThreads % 32 == 0 && kThreads >= 128 && kThreads <= 256, "block size");
+static_assert(kSmallMaxM <= kCandHigh, "candidate list sizing");
+static_assert(kMaxStreamCluster * kSmallMaxM <= kMergeCap, "cluster merge sizing");
 static_assert(kTile % kChunk == 0, "chunking");
+static_assert(2 * kCandCap * 4 <= kCandCap * 8 && kCandCap * 8 <= kStages * kTile * 4, "finish buffers alias list and ring");
 
 enum : int { MODE_SAMPLE = 0, MODE_LOCAL_TOPM = 1, MODE_MERGE = 2 };
 
@@ -94,6 +109,7 @@ struct __align__(16) StreamSmem {
   int cand_count;
   int pen_unique;
   int misc[2];
+  float vbp[2];  // value buckets (lo, scale) of the candidates collected with a guessed threshold
   // followed by the penalty hash table: pen_slots ints
 };
 
@@ -119,7 +135,7 @@ __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) 
 // of the window early, so that the global load is in flight while other work goes on.
 __device__ __forceinline__ void pen_clear(int *tab, int slots, int *unique_ctr, uint32_t *bloom) {
   for (int i = threadIdx.x; i < slots; i += kThreads) tab[i] = kPenEmpty;
-  if (threadIdx.x < kPenBloomBits / 32) bloom[threadIdx.x] = 0u;
+  for (int i = threadIdx.x; i < kPenBloomBits / 32; i += kThreads) bloom[i] = 0u;
   if (threadIdx.x == 0) *unique_ctr = 0;
 }
 __device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_total, int *status,
@@ -158,7 +174,7 @@ __device__ unsigned long long block_select_pivot(const unsigned long long *c, in
   unsigned long long prefix = 0, mask = 0;
   uint32_t need = (uint32_t)want;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  hist[threadIdx.x] = 0;  // kThreads == 256
+  for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
   __syncthreads();
   for (int shift = 56; shift >= 0; shift -= 8) {
 #pragma unroll 1
@@ -241,10 +257,172 @@ __device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int 
   return block_compact(c, n, pivot, counter);
 }
 
+// ---- linear value buckets: a cheap coarse order for short lists -------------------------------------------------
+// 256 equal-width buckets upwards from `lo`.  The mapping is monotone (a larger value never lands in a lower
+// bucket) whatever the inputs, because subtraction, multiplication by a non-negative scale, conversion and
+// clamping all are: NaN, -inf and everything <= lo end up in bucket 0, +inf and everything beyond the last
+// bucket in 255; a degenerate scale (0, inf or NaN) only makes the order coarser.
+struct ValueBuckets {
+  float lo, scale;
+  __device__ __forceinline__ void set(float lo_, float hi_) {
+    lo = fmaxf(lo_, -3.402823466e38f);
+    scale = __fdividef(255.f, fminf(hi_, 3.402823466e38f) - lo);
+    if (!(scale >= 0.f)) scale = 0.f;
+  }
+  __device__ __forceinline__ int of(float v) const {
+    const int b = __float2int_rz((v - lo) * scale);  // NaN converts to 0
+    return b < 0 ? 0 : (b > 255 ? 255 : b);
+  }
+  __device__ __forceinline__ int of_key(uint32_t key) const { return of(key2f(key)); }
+};
+
+// Warp 0, after a barrier: lane l owns bins 8l .. 8l+7 of hist.  Returns the lane's bin counts, their sum and the
+// number of entries in the bins of higher lanes.
+__device__ __forceinline__ void warp_bins_above(const uint32_t *hist, int lane, uint32_t (&loc)[8], uint32_t &own,
+                                                uint32_t &above) {
+  own = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { loc[k] = hist[8 * lane + k]; own += loc[k]; }
+  uint32_t suf = own;  // inclusive suffix sum over lanes >= lane
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const uint32_t t = __shfl_down_sync(0xffffffffu, suf, o);
+    if (lane + o < 32) suf += t;
+  }
+  above = suf - own;
+}
+
+// block-wide minimum and maximum of per-thread keys (sel[0], sel[1]); keys <= 1 (no entry, NaN) are left out by
+// the caller passing mn = 0xffffffff / mx = 0.  Ends with a barrier.
+__device__ __forceinline__ void block_key_range(uint32_t mn, uint32_t mx, uint32_t *sel) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = min(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((threadIdx.x & 31) == 0) { atomicMin(&sel[0], mn); atomicMax(&sel[1], mx); }
+  __syncthreads();
+}
+
+// A value that roughly `r` of the 2 * kThreads sampled maxima (two per thread, m1 >= m2) reach or exceed: the lower
+// edge of the value bucket that holds the r-th largest.  It is a guess (the caller checks what it collects with
+// it); NaN means "no guess" (a flat or non-finite sample).  r <= kThreads.  hist must be zero on entry (it is
+// left zero), sel[0] = 0xffffffff, sel[1] = 0, sel[3] = NaN bits, and a barrier must lie between that set-up and this call.
+// vb_out[0..1] receive the buckets (lo, scale) that the candidates above the guess are later sorted with: from the
+// guess up to as far above the sample's maximum as that lies above the guess.
+__device__ float block_guess_threshold(float m1, float m2, int r, uint32_t *hist, uint32_t *sel, float *vb_out) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t k1 = f2key(m1);
+  block_key_range(k1, k1, sel);
+  ValueBuckets vb;
+  // at least kThreads values (every m1) reach the smallest m1, so the r-th largest lies in [min m1, max m1]
+  vb.set(key2f(sel[0]), key2f(sel[1]));
+  const float smin = key2f(sel[0]), smax = key2f(sel[1]);
+  const bool usable = smax > smin && vb.scale > 0.f && vb.scale < 3.402823466e38f;  // false for NaN too
+  if (!usable) return __int_as_float(0x7fc00000);
+  atomicAdd(&hist[vb.of(m1)], 1u);
+  atomicAdd(&hist[vb.of(m2)], 1u);
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t loc[8], own, above;
+    warp_bins_above(hist, lane, loc, own, above);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) hist[8 * lane + k] = 0;
+    if (above < (uint32_t)r && (uint32_t)r <= above + own) {
+      uint32_t acc = above;
+      int bin = 8 * lane;
+#pragma unroll
+      for (int k = 7; k >= 0; --k) {
+        acc += loc[k];
+        if (acc >= (uint32_t)r) { bin = 8 * lane + k; break; }
+      }
+      bin = bin > 254 ? 254 : bin;  // ties at the maximum must still pass a strict compare
+      const float guess = smin + (float)bin * __fdividef(smax - smin, 255.f);
+      sel[3] = __float_as_uint(guess);
+      ValueBuckets later;
+      later.set(guess, smax + (smax - guess));
+      vb_out[0] = later.lo;
+      vb_out[1] = later.scale;
+    }
+  }
+  __syncthreads();
+  return __uint_as_float(sel[3]);
+}
+
+// Orders the `want` largest of c[0..n) (all of them when n <= want) into out[0..) by composite, descending, and
+// returns how many that is; tmp (n entries) overlaps neither c nor out, but out may be c itself.  A counting sort over linear value buckets
+// between the smallest and the largest key brings the list into coarse order in tmp; the final position of an
+// entry is the start of its bucket plus the number of larger composites inside the bucket, which is a short walk
+// unless many entries share a bucket (ties, one huge outlier).  Then nothing is written and -1 comes back, and
+// the caller takes the radix path.  All threads call it.
+constexpr int kBucketWalkMax = 96;
+__device__ int block_top_sorted(const unsigned long long *c, int n, int want, unsigned long long *tmp,
+                                unsigned long long *out, uint32_t *hist, uint32_t *sel, const float *prepared) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  ValueBuckets vb;
+  if (prepared) {
+    // the caller counted the entries into hist under these buckets while it collected them
+    vb.lo = prepared[0];
+    vb.scale = prepared[1];
+  } else {
+    for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
+    if (threadIdx.x == 0) { sel[0] = 0xffffffffu; sel[1] = 0u; }
+    __syncthreads();
+    uint32_t mn = 0xffffffffu, mx = 0u;
+#pragma unroll 1
+    for (int i = threadIdx.x; i < n; i += kThreads) {
+      const uint32_t k = comp_key(c[i]);
+      if (k > 1u) { mn = min(mn, k); mx = max(mx, k); }
+    }
+    block_key_range(mn, mx, sel);
+    vb.set(key2f(sel[0]), key2f(sel[1]));  // no valid key at all: NaN bounds, every entry in bucket 0
+#pragma unroll 1
+    for (int i = threadIdx.x; i < n; i += kThreads) atomicAdd(&hist[vb.of_key(comp_key(c[i]))], 1u);
+    __syncthreads();
+  }
+  if (warp == 0) {  // counts -> start of each bucket in descending order (entries in higher buckets)
+    uint32_t loc[8], own, above;
+    warp_bins_above(hist, lane, loc, own, above);
+    uint32_t acc = above, big = 0;
+#pragma unroll
+    for (int k = 7; k >= 0; --k) {
+      hist[8 * lane + k] = acc;
+      if (acc < (uint32_t)want) big = max(big, loc[k]);  // only buckets that reach into the wanted part are walked
+      acc += loc[k];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big = max(big, __shfl_xor_sync(0xffffffffu, big, o));
+    if (lane == 0) sel[2] = big;
+  }
+  __syncthreads();
+  if (sel[2] > (uint32_t)kBucketWalkMax) return -1;
+#pragma unroll 1
+  for (int i = threadIdx.x; i < n; i += kThreads) {
+    const unsigned long long e = c[i];
+    tmp[atomicAdd(&hist[vb.of_key(comp_key(e))], 1u)] = e;
+  }
+  __syncthreads();  // hist[b] is now the end of bucket b, which is the start of bucket b - 1
+#pragma unroll 1
+  for (int q = threadIdx.x; q < n; q += kThreads) {
+    const unsigned long long e = tmp[q];
+    const int b = vb.of_key(comp_key(e));
+    const int from = b == 255 ? 0 : (int)hist[b + 1], to = (int)hist[b];
+    if (from < want) {
+      int rank = from;
+#pragma unroll 2
+      for (int j = from; j < to; ++j) rank += (tmp[j] > e) ? 1 : 0;
+      if (rank < want) out[rank] = e;
+    }
+  }
+  __syncthreads();
+  return n < want ? n : want;
+}
+
 // ---- the finish: penalty, order, softmax, cut, draw (leader CTA) ----------------------------------------------
-// cand[0..n): a superset of the candidates the reference would hold, unordered (exactly its M largest raw
-// entries when the caller had to cut to M).  `sorted` (kCandCap composites) must not overlap cand; ev / pv
-// (kCandCap floats each) may alias cand, which is dead once `sorted` is written.
+// cand[0..n), n <= kCandCap: a superset of the candidates the reference would hold, unordered (exactly its M largest
+// raw entries when the caller had to cut to M).  `ring` is the kCandCap composites that follow the list in shared
+// memory; list and ring are both scratch from here on.  `penalised`: the list already holds penalised values.
+// `prepared`: value buckets (lo, scale) under which S.hist already counts the list's entries, or nullptr.
 // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied.  All threads call it.
 __device__ __forceinline__ void penalise_candidates(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
                                                     const uint32_t *bloom, float rp) {
@@ -262,20 +440,49 @@ __device__ __forceinline__ void penalise_candidates(unsigned long long *cand, in
   __syncthreads();
 }
 
+// The same in one pass with a count of the (penalised) entries by value bucket (vbp: lo, scale) into hist, which
+// must be zero on entry.
+__device__ __forceinline__ void penalise_and_count(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
+                                                   const uint32_t *bloom, bool any_pen, float rp, const float *vbp,
+                                                   uint32_t *hist) {
+  ValueBuckets vb;
+  vb.lo = vbp[0];
+  vb.scale = vbp[1];
+#pragma unroll 1
+  for (int i = threadIdx.x; i < n; i += kThreads) {
+    const unsigned long long c = cand[i];
+    const int id = comp_id(c);
+    float v = key2f(comp_key(c));
+    const uint32_t b = pen_bloom_bit(id);
+    if (any_pen && ((bloom[b >> 5] >> (b & 31)) & 1u) && pen_contains(pen_tab, pen_slots, id)) {
+      v = v > 0.f ? __fdiv_rn(v, rp) : __fmul_rn(v, rp);
+      cand[i] = make_comp(f2key(v), (uint32_t)id);
+    }
+    atomicAdd(&hist[vb.of(v)], 1u);
+  }
+  __syncthreads();
+}
+
 __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
-                           const int *pen_tab, int npen, unsigned long long *sorted, float *ev, float *pv,
-                           StreamSmem &S, long long *clk, bool penalised = false) {
+                           const int *pen_tab, int npen, unsigned long long *ring, StreamSmem &S, long long *clk,
+                           bool penalised, const float *prepared) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // the RNG words of a possible draw: requested now, used after the ordering and the softmax
   MtFetch rng = {};
   if (threadIdx.x == 0 && a.draw && p.temperature > 0.f) rng = mt_fetch(a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
   if (npen > 0 && !penalised) penalise_candidates(cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
   if (clk) clk[11] = clock64();
-  // the K best by (value desc, id asc) (sampler.cpp:43-44): select, then rank = number of larger composites
-  n = block_keep_top(cand, n, K, S.hist, S.sel, &S.cand_count);
+  // the K best by (value desc, id asc) (sampler.cpp:43-44), in order
+  unsigned long long *sorted = cand;
+  float *ev = reinterpret_cast<float *>(ring), *pv = ev + kCandCap;
+  int nK = block_top_sorted(cand, n, K, ring, sorted, S.hist, S.sel, prepared);
   if (clk) clk[12] = clock64();
-  const int nK = n;
-  {
+  if (nK < 0) {
+    // crowded buckets: radix select, then rank = number of larger composites
+    nK = block_keep_top(cand, n, K, S.hist, S.sel, &S.cand_count);
+    sorted = ring;
+    ev = reinterpret_cast<float *>(cand);
+    pv = ev + kCandCap;
     // P lanes share one entry (P = 32, 16, 8, 4, 2 or 1, as many as the CTA can spare), each counting over a
     // strided part of the list; partial ranks are summed with shuffles
     int P = 32;
@@ -290,8 +497,8 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
       for (int o = P >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
       if (i < nK && sub == 0) sorted[rank] = c;
     }
+    __syncthreads();
   }
-  __syncthreads();
   if (clk) clk[5] = clock64();
 
   const bool greedy = p.temperature <= 0.f;
@@ -314,60 +521,130 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
   if (clk) clk[6] = clock64();
   if (warp != 0) return;
 
-  // Ordered double arithmetic, replayed exactly: every lane of warp 0 carries the same running values.
+  // Warp 0 replays the reference's ordered double arithmetic (sampler.cpp:47-63) without walking it entry by
+  // entry where the outcome cannot depend on the order:
+  //  * sums of the float numerators: with the smallest of them >= 2^-20 and at most 512 of them (none above 1),
+  //    every partial sum in any order is a multiple of 2^-43 below 2^10, hence exact in double, so a tree gives
+  //    the sequential result bit for bit;
+  //  * running sums that are only compared (cumulative probability against top_p, the draw against the
+  //    cumulative distribution): prefix sums in another order differ from the sequential ones by less than
+  //    1e-13, so a comparison that is not within 1e-12 of equality has the same outcome.
+  // Anything else (tiny numerators, a comparison within 1e-12) takes the sequential walk.
+  constexpr double kEps = 1e-12;
+  const int per = (nK + 31) >> 5;  // consecutive entries per lane
+  const int j0 = min(nK, lane * per), j1 = min(nK, j0 + per);
+  const bool exact_sums = ev[nK - 1] >= 0x1p-20f;  // ev is descending
+  double *qd = reinterpret_cast<double *>(sorted + 512);  // nK <= 500 entries of sorted are in use, 512 more follow
   double sum = 0.0;
+  if (exact_sums) {
+#pragma unroll 1
+    for (int j = j0; j < j1; ++j) sum += (double)ev[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  } else {
 #pragma unroll 4
-  for (int j = 0; j < nK; ++j) sum += (double)ev[j];
+    for (int j = 0; j < nK; ++j) sum += (double)ev[j];
+  }
   if (clk) clk[13] = clock64();
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
   const bool use_minp = p.min_p > 0.f;
   const double top_p = (double)p.top_p;
-  int keep = nK;
-  double cum = 0.0;
-  bool done = false;
-  double *qs = reinterpret_cast<double *>(S.hist);  // 32 quotients of the current chunk (the histogram is idle)
-  for (int base = 0; base < nK && !done; base += 32) {  // sampler.cpp:48-52, 32 positions at a time
-    const int i = base + lane;
-    const float e = i < nK ? ev[i] : 0.f;
-    qs[lane] = __ddiv_rn((double)e, sum);
-    const bool fail = use_minp && i < nK && e < minp_thr;
-    const uint32_t failmask = __ballot_sync(0xffffffffu, fail);
-    const int cnt = nK - base < 32 ? nK - base : 32;
-    __syncwarp();
-    // the running sum is a dependent chain of double adds; without branches inside, its loads and compares overlap
-    int first_top = 32;
-#pragma unroll 8
-    for (int j = 0; j < 32; ++j) {
-      const double next = cum + qs[j];
-      const bool valid = j < cnt;
-      cum = valid ? next : cum;
-      first_top = (valid && first_top == 32 && next >= top_p) ? j : first_top;
+  // lane-local pass: quotients, their sum, entries that pass min-p (a prefix: ev is descending)
+  double lt = 0.0;
+  int passes = 0;
+#pragma unroll 1
+  for (int j = j0; j < j1; ++j) {
+    const float e = ev[j];
+    const double q = __ddiv_rn((double)e, sum);
+    qd[j] = q;
+    lt += q;
+    passes += (use_minp && e < minp_thr) ? 0 : 1;
+  }
+  auto warp_exclusive = [&](double v) {  // sum of v over lower lanes
+    double incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
     }
-    const int first_fail = failmask ? __ffs(failmask) - 1 : 32;
+    const double prev = __shfl_up_sync(0xffffffffu, incl, 1);
+    return lane == 0 ? 0.0 : prev;
+  };
+  int keep;
+  {
+    double c = warp_exclusive(lt);
+    int below = 0;
+    bool amb = false;
+#pragma unroll 1
+    for (int j = j0; j < j1; ++j) {
+      c += qd[j];
+      below += (c < top_p) ? 1 : 0;
+      amb |= (j < nK - 1) && (fabs(c - top_p) <= kEps);  // at the last entry both outcomes keep everything
+    }
+    const int first_fail = __reduce_add_sync(0xffffffffu, passes);  // == nK: nothing fails
+    int first_top = __reduce_add_sync(0xffffffffu, below);          // == nK: never reached
+    if (__any_sync(0xffffffffu, amb)) {  // sampler.cpp:48-52 entry by entry
+      __syncwarp();
+      double cum = 0.0;
+      first_top = nK;
+#pragma unroll 1
+      for (int j = 0; j < nK; ++j) {
+        cum += qd[j];
+        if (cum >= top_p) { first_top = j; break; }
+      }
+    }
     // position i: the min-p test comes first, then the sum test (sampler.cpp:50-51)
-    if (first_fail <= first_top && first_fail < 32) { keep = base + first_fail > 1 ? base + first_fail : 1; done = true; }
-    else if (first_top < 32) { keep = base + first_top + 1; done = true; }
-    __syncwarp();
+    if (first_fail < nK && first_fail <= first_top) keep = first_fail > 1 ? first_fail : 1;
+    else if (first_top < nK) keep = first_top + 1;
+    else keep = nK;
   }
   if (clk) clk[15] = clock64();
-  double tot = 0.0;
+  const int k1 = min(j1, keep);
+  double tot = 0.0;  // sampler.cpp:54
+  if (exact_sums) {
+#pragma unroll 1
+    for (int j = j0; j < k1; ++j) tot += (double)ev[j];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  } else {
 #pragma unroll 4
-  for (int j = 0; j < keep; ++j) tot += (double)ev[j];  // sampler.cpp:54
-  for (int j = lane; j < keep; j += 32) pv[j] = __double2float_rn(__ddiv_rn((double)ev[j], tot));  // :55
+    for (int j = 0; j < keep; ++j) tot += (double)ev[j];
+  }
+  double pl = 0.0;
+#pragma unroll 1
+  for (int j = j0; j < k1; ++j) {  // sampler.cpp:55
+    const float pj = __double2float_rn(__ddiv_rn((double)ev[j], tot));
+    pv[j] = pj;
+    pl += (double)pj;
+  }
   __syncwarp();
   if (clk) clk[3] = clock64();
-  // draw (sampler.cpp:58-63)
+  // draw (sampler.cpp:58-63): the first entry at which the variate, less the probabilities so far, is <= 0
   int pick = 0;
   if (keep > 1 && a.draw) {
     unsigned long long w = 0;
     if (lane == 0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
     w = __shfl_sync(0xffffffffu, w, 0);
-    double r = word_to_uniform(w);
-    pick = keep - 1;
+    const double r = word_to_uniform(w);
+    double c = warp_exclusive(pl);
+    int below = 0;
+    bool amb = false;
 #pragma unroll 1
-    for (int j = 0; j < keep; ++j) {
-      r -= (double)pv[j];
-      if (r <= 0.0) { pick = j; break; }
+    for (int j = j0; j < k1; ++j) {
+      c += (double)pv[j];
+      below += (c < r) ? 1 : 0;
+      amb |= (j < keep - 1) && (fabs(c - r) <= kEps);  // the last entry is picked whatever is left
+    }
+    pick = __reduce_add_sync(0xffffffffu, below);
+    pick = pick < keep - 1 ? pick : keep - 1;
+    if (__any_sync(0xffffffffu, amb)) {
+      double rr = r;
+      pick = keep - 1;
+#pragma unroll 1
+      for (int j = 0; j < keep; ++j) {
+        rr -= (double)pv[j];
+        if (rr <= 0.0) { pick = j; break; }
+      }
     }
   }
   if (lane == 0) {

@@ -17,7 +17,7 @@
 namespace qpb {
 
 template <int MODE, bool TIMED = false>
-__global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
   int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
@@ -70,8 +70,15 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // It is a guess: if fewer columns pass than are needed, the piece is streamed again without it.
     const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kStages;
     int g0 = g_next;  // ring slot of the piece's tile 0 (moved past the sample below)
-    if (tid == 0)
+    if (tid == 0) {
       for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, g0 + j);
+      // The ring only holds kStages tiles, so HBM would sit idle while the threshold is worked out: ask for the
+      // next few (full) tiles of the piece to be brought into L2 meanwhile.
+      if (can_boot && kBootPrefetchTiles > 0) {
+        const int np = min(kBootPrefetchTiles, n_tiles - 2);
+        bulk_prefetch_l2(rowp + s0 + kTile, (uint32_t)np * kTile * 4u);
+      }
+    }
 
     // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
     // (the RNG words are only pulled towards L2 here: holding them in registers through the scan costs occupancy)
@@ -111,6 +118,8 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // check afterwards that K of them still exceed it once penalised.
     const bool lean = npieces == 1 && MODE == MODE_SAMPLE && (!use_pen || p.repeat_penalty >= 1.f);
     bool shrunk = false, penalised = false;
+    bool have_vb = false;  // S.vbp holds value buckets for the columns above the guessed threshold, S.hist is zero
+    bool hist_ok = false;  // S.hist counts the (penalised) list by those buckets
     int n = 0;  // entries of the list once it is final
 
     // A column is a candidate unless it is <= thr: while thr is NaN every column is taken; afterwards thr is the
@@ -135,6 +144,8 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
           }
         }
       }
+      for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;  // set-up of block_guess_threshold
+      if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
       __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
       g0 += kStages;    // start the stream proper while the threshold is worked out (its tiles are fetched again)
       if (tid == 0)
@@ -144,15 +155,12 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       const long long sample = (long long)kStages * kTile;
       const long long aim = lean ? min((long long)Mloc, (long long)K + 16 + K / 4) : (long long)Mloc;
       long long r = (9LL * aim * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
-      r = r < (lean ? 12 : 16) ? (lean ? 12 : 16) : r;
-      booted = Mloc < Vt && r <= 200;  // two maxima per thread hold the sample's best couple of hundred well enough
+      r = r < (lean ? kLeanMinRank : 16) ? (lean ? kLeanMinRank : 16) : r;
+      booted = Mloc < Vt && r <= kThreads * 3 / 4;  // two maxima per thread hold the sample's best few dozen well enough
       if (booted) {
-        S.cand[2 * tid] = make_comp(f2key(m1), (uint32_t)(2 * tid));
-        S.cand[2 * tid + 1] = make_comp(f2key(m2), (uint32_t)(2 * tid + 1));
-        __syncthreads();
-        const unsigned long long pivot = block_select_pivot(S.cand, 2 * kThreads, (int)r, S.hist, S.sel);
-        thr = key2f((uint32_t)(pivot >> 32));  // a lower bound of the r-th largest; key 0 gives NaN = no threshold
-        __syncthreads();                        // the list is free again
+        thr = block_guess_threshold(m1, m2, (int)r, S.hist, S.sel, S.vbp);  // NaN: no usable guess
+        booted = thr == thr;
+        have_vb = booted;
       }
     }
     QPB_STAMP(1);
@@ -160,6 +168,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // keep the Mloc best of the list and raise the threshold to the weakest of them; all threads call it
     auto shrink = [&]() {
       shrunk = true;
+      have_vb = false;
       const long long c0 = clk ? clock64() : 0;
       block_keep_top(S.cand, min(S.cand_count, kCandCap), Mloc, S.hist, S.sel, &S.cand_count);
       // later columns must beat the weakest kept key: an equal key at a higher index loses.  The select may stop
@@ -175,6 +184,11 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       __syncthreads();
       thr = key2f(S.sel[3]);  // key 1 (a NaN is among the kept) maps back to NaN: keep taking everything
       if (clk) { select_clk += clock64() - c0; ++n_selects; }
+    };
+
+    // one survivor into list slot `pos` (dropped beyond the capacity: the caller notices the count)
+    auto put = [&](int pos, float x, int id) {
+      if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(x), (uint32_t)id));
     };
 
     // ---- streaming phase ----
@@ -198,11 +212,11 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
           const int cnt_before = S.cand_count;
           const uint32_t stage_s = ring_s + (uint32_t)st * (kTile * 4u);
           const uint32_t lane_s = stage_s + (uint32_t)tid * 16u;
-          uint32_t mask = 0;  // bit 4c + j: column c * 1024 + tid * 4 + j of the tile survives
+          uint32_t mask = 0;  // bit 4c + j: column c * kChunk + tid * 4 + j of the tile survives
           mask_not_le<0>(lds_f4(lane_s), thr, mask);
-          mask_not_le<4>(lds_f4(lane_s + 4096u), thr, mask);
-          mask_not_le<8>(lds_f4(lane_s + 8192u), thr, mask);
-          mask_not_le<12>(lds_f4(lane_s + 12288u), thr, mask);
+          mask_not_le<4>(lds_f4(lane_s + kThreads * 16u), thr, mask);
+          mask_not_le<8>(lds_f4(lane_s + kThreads * 32u), thr, mask);
+          mask_not_le<12>(lds_f4(lane_s + kThreads * 48u), thr, mask);
           const uint32_t lanes = __ballot_sync(0xffffffffu, mask != 0u);
           if (lanes != 0u) {
             // Same-address shared-memory atomics serialise and a warp scan is not free either: a warp with few
@@ -227,9 +241,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
               const int e = __ffs(mask) - 1;
               mask &= mask - 1u;
               const int off = (e >> 2) * (kThreads * 4) + tid * 4 + (e & 3);
-              if (pos < kCandCap)
-                smem_store_u64(&S.cand[pos], make_comp(f2key(lds_f32(stage_s + (uint32_t)off * 4u)),
-                                                        (uint32_t)(a.id_offset + tbase + off)));
+              put(pos, lds_f32(stage_s + (uint32_t)off * 4u), a.id_offset + tbase + off);
               ++pos;
             }
           }
@@ -305,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
                 const int e = __ffs(accmask) - 1;
                 accmask &= accmask - 1u;
                 const int off = tid * 4 + e;
-                if (pos < kCandCap) smem_store_u64(&S.cand[pos], make_comp(f2key(src[off]), (uint32_t)(qbase + off)));
+                put(pos, src[off], qbase + off);
                 ++pos;
               }
             }
@@ -358,8 +370,16 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
           if (csize == 1) {
             const int nl = min(S.cand_count, kCandCap);
             build_pen_now();
-            if (npen > 0) penalise_candidates(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
-            ok = count_above(nl, f2key(thr)) >= min(K, s1 - s0);
+            if (have_vb) {
+              // one pass penalises the list and counts it into the value buckets laid out with the guess; bucket 0
+              // is "not above the guess"
+              penalise_and_count(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, npen > 0, p.repeat_penalty, S.vbp, S.hist);
+              ok = nl - (int)S.hist[0] >= min(K, s1 - s0);
+              hist_ok = ok;
+            } else {
+              if (npen > 0) penalise_candidates(S.cand, nl, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
+              ok = count_above(nl, f2key(thr)) >= min(K, s1 - s0);
+            }
             penalised = ok;
           } else {
             guess = true;  // the leader judges the merged list
@@ -414,7 +434,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
       }
       if (ok) break;
       __syncthreads();
-      booted = false;
+      booted = have_vb = hist_ok = false;
       thr = __int_as_float(0x7fc00000);
       if (tid == 0) {
         S.cand_count = 0;
@@ -521,10 +541,8 @@ __global__ void __launch_bounds__(kThreads, 4) stream_rows_kernel(const __grid_c
     // raw cut can be skipped; a penalty below 1 raises values and needs it.
     if (npen > 0 && !(p.repeat_penalty >= 1.f)) n = block_keep_top(S.cand, n, M, S.hist, S.sel, &S.cand_count);
 
-    unsigned long long *sorted = reinterpret_cast<unsigned long long *>(&S.ring[0][0]);
-    float *ev = reinterpret_cast<float *>(&S.cand[0]);
-    float *pv = ev + kCandCap;
-    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, sorted, ev, pv, S, clk, penalised);
+    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, reinterpret_cast<unsigned long long *>(&S.ring[0][0]), S, clk, penalised,
+               (hist_ok && penalised) ? S.vbp : nullptr);
     QPB_STAMP(7);
     __syncthreads();  // the ring (sorted) and the list are free for the next piece
     if (tid == 0) S.cand_count = 0;

@@ -114,7 +114,8 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
     if (w > maxw) maxw = w;
     const bool greedy = p.temperature <= 0.f;
     const long long K = greedy ? 1 : (p.top_k > 0 ? (p.top_k < vocab_total ? p.top_k : vocab_total) : vocab_total);
-    (K + w <= kSmallMaxM ? a : b).push_back(r);
+    // the streaming kernel takes rows with a small budget that is also below the "whole row" mark of top_m
+    (K + w <= kSmallMaxM && K + w < vocab_total / 4 ? a : b).push_back(r);
   }
   s->n_stream = (int)a.size();
   s->n_whole = (int)b.size();
@@ -129,9 +130,9 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
 }
 
 int pick_cluster(const qpb_sampler *s, int rows) {
-  if (s->cluster) return s->cluster;
+  if (s->cluster) return s->cluster < kMaxStreamCluster ? s->cluster : kMaxStreamCluster;
   // one CTA per row as soon as a handful of rows are in flight; a cluster only pays for a few rows
-  return rows <= 8 ? 8 : 1;
+  return rows <= 8 ? kMaxStreamCluster : 1;
 }
 
 template <int MODE>
@@ -632,8 +633,8 @@ int qpb_sampler_cand_slots(qpb_sampler *s, int vocab_total, int vocab_local_max,
   long long m = 1;
   for (const auto &p : s->h_params) {
     long long b = row_budget(p, vocab_total);
-    if (b > kSmallMaxM) return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 500");
-    if (b >= vocab_total / 4) b = vocab_total;
+    if (b > kSmallMaxM || b >= vocab_total / 4)
+      return fail(s, QPB_ERR_UNSUPPORTED, "vocab-sharded rows need top_k + window <= 500 and below a quarter of the vocabulary");
     if (b > m) m = b;
   }
   if (m > vocab_local_max) m = vocab_local_max;
@@ -670,7 +671,7 @@ int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_s
                              int32_t *d_dist_count, int max_out, int32_t *d_out_ids, void *stream) {
   if (!s) return QPB_ERR_INVALID;
   if (!d_cand_all || n_shards <= 0 || slots <= 0) return fail(s, QPB_ERR_INVALID, "candidate buffer invalid");
-  if ((long long)n_shards * slots > kMergeCap) return fail(s, QPB_ERR_UNSUPPORTED, "n_shards * slots exceeds 8192");
+  if ((long long)n_shards * slots > kMergeCap) return fail(s, QPB_ERR_UNSUPPORTED, "n_shards * slots exceeds the merge list");
   if (!d_out_ids && !d_dist_count) return fail(s, QPB_ERR_INVALID, "no output requested");
   Inputs in{nullptr, 0, n_rows, vocab_total, vocab_total, 0, d_history, hist_stride, d_hist_len, hist_len_all};
   int rc = check_inputs(s, in, false);
@@ -770,8 +771,8 @@ int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, con
     if (w > max_window) max_window = w;
     const bool greedy = p.temperature <= 0.f;
     const long long K = greedy ? 1 : (p.top_k > 0 ? (p.top_k < vocab ? p.top_k : vocab) : vocab);
-    if (K + w > kSmallMaxM) {
-      static_msg(errbuf, errbuf_len, "top_k + history window exceeds 500: such rows need the handle-based entry points");
+    if (K + w > kSmallMaxM || K + w >= vocab / 4) {
+      static_msg(errbuf, errbuf_len, "top_k + history window exceeds 500 or a quarter of the vocabulary: such rows need the handle-based entry points");
       return QPB_ERR_UNSUPPORTED;
     }
   }
