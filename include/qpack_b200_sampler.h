@@ -117,6 +117,12 @@ QPB_API int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state
 /* Thread-block cluster size used per row: 0 = choose from the row count (default), else 1 to 8. */
 QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
 
+/* Streaming kernel configuration (tuning and tests; no counterpart in the reference): threads per CTA (128 or 256)
+ * and log2 of the shared-memory ring depth (1 to 3).  0 = chosen per launch from the number of rows (default):
+ * 256 threads with the deepest ring that fits for up to four CTAs per SM, 128 threads and eight CTAs per SM beyond.
+ * With 128 threads a cluster holds at most 4 CTAs. */
+QPB_API int qpb_sampler_set_stream_config(qpb_sampler *s, int threads, int log2_stages);
+
 /* Row pieces: the tiles of all rows of a call laid end to end and dealt out in equal runs to as many CTAs as fit on
  * the GPU, rows that straddle two CTAs merged through device scratch (allocated on first use).  mode 0 (default):
  * only when whole rows would leave the last wave of CTAs less than a quarter full; 1: always; -1: never. */

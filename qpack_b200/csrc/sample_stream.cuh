@@ -22,38 +22,16 @@
 namespace qpb {
 namespace cg = cooperative_groups;
 
-#ifndef QPB_STREAM_THREADS
-#define QPB_STREAM_THREADS 256
-#endif
-constexpr int kThreads = QPB_STREAM_THREADS;  // threads per CTA; the other sizes follow from it
-constexpr int kCtasPerSm = 1024 / kThreads;   // resident CTAs per SM the kernel is built for (64 registers a thread)
-constexpr int kTile = kThreads * 16;          // floats per ring stage: four float4 per thread
-constexpr int kStages = 2;                    // ring depth; kStages * kTile * 4 bytes in flight per CTA
-constexpr int kChunk = kThreads * 4;          // careful mode scans a tile in chunks of one float4 per thread
-constexpr int kCandCap = kThreads * 8;        // candidate entries of the streaming phase
-constexpr int kCandHigh = kCandCap - kChunk;  // careful mode: select when the list grows beyond this (a chunk adds <= kChunk)
-constexpr int kCandHighFast = kThreads * 5;   // fast mode: select after a tile that left more than this
-constexpr int kRingEntries = kStages * kTile * 4 / 8;
-constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to a merge (the ring is reused)
 // Rows with top_k + window above this take the whole-row kernel instead, and so do rows whose budget reaches a
 // quarter of the vocabulary (top_m then returns the whole row, sampler.cpp:14): the host routes them away.
 constexpr int kSmallMaxM = 500;
-constexpr int kMaxStreamCluster = kMergeCap / kSmallMaxM >= 8 ? 8 : 4;  // CTAs whose lists fit the leader's merge
-#ifndef QPB_BOOT_PREFETCH_TILES
-#define QPB_BOOT_PREFETCH_TILES 0
-#endif
-#ifndef QPB_LEAN_MIN_RANK
-#define QPB_LEAN_MIN_RANK 12
-#endif
-constexpr int kBootPrefetchTiles = QPB_BOOT_PREFETCH_TILES;  // tiles asked into L2 while the threshold is bootstrapped
-constexpr int kLeanMinRank = QPB_LEAN_MIN_RANK;              // lowest sample rank a lean threshold is taken at
-constexpr int kPenBloomBits = 4096;          // one-probe negative test in front of the penalty hash table
+constexpr int kLeanMinRank = 12;      // lowest sample rank a lean threshold is taken at
+constexpr int kSampleTiles = 2;       // tiles fetched ahead of the stream to guess a threshold from
+constexpr int kMinStages = 2;         // ring stages every configuration has (the merge and the finish reuse them)
+constexpr int kMaxStages = 8;         // deepest ring (a power of two, like every ring depth)
+constexpr int kPenBloomBits = 4096;   // one-probe negative test in front of the penalty hash table
 constexpr int kPenEmpty = -1;
-static_assert(kThreads % 32 == 0 && kThreads >= 128 && kThreads <= 256, "block size");
-static_assert(kSmallMaxM <= kCandHigh, "candidate list sizing");
-static_assert(kMaxStreamCluster * kSmallMaxM <= kMergeCap, "cluster merge sizing");
-static_assert(kTile % kChunk == 0, "chunking");
-static_assert(2 * kCandCap * 4 <= kCandCap * 8 && kCandCap * 8 <= kStages * kTile * 4, "finish buffers alias list and ring");
+constexpr int kBucketWalkMax = 96;    // longest walk inside one value bucket before the radix path takes over
 
 enum : int { MODE_SAMPLE = 0, MODE_LOCAL_TOPM = 1, MODE_MERGE = 2 };
 
@@ -84,6 +62,7 @@ struct StreamArgs {
   int n_shards;
   int cand_rows;           // row dimension of cand_io
   int pen_slots;           // penalty hash slots (power of two)
+  int log2_stages;         // ring depth = 1 << log2_stages (1 .. 3)
   // Row pieces (one CTA per cluster only).  units_per_cta > 0: the rows of this launch, cut into tiles of kTile
   // columns and laid end to end, are dealt out in equal runs of units_per_cta tiles to the CTAs of the grid; a row
   // that straddles CTAs is sampled in pieces, each piece leaves its best candidates in piece_cand, and the CTA
@@ -96,21 +75,6 @@ struct StreamArgs {
   int *piece_done;                  // [rows], zero between launches (the finishing CTA resets it)
   int *status;
   long long *phase_clk;    // optional [rows][16]: SM clock stamps of the leader CTA's phases (latency breakdown)
-};
-
-struct __align__(16) StreamSmem {
-  unsigned long long cand[kCandCap];  // candidates; the ring follows directly so that the merge can use both
-  float ring[kStages][kTile];
-  uint64_t full[kStages];
-  unsigned long long exp_tab[32];
-  uint32_t hist[256];
-  uint32_t pen_bloom[kPenBloomBits / 32];
-  uint32_t sel[4];
-  int cand_count;
-  int pen_unique;
-  int misc[2];
-  float vbp[2];  // value buckets (lo, scale) of the candidates collected with a guessed threshold
-  // followed by the penalty hash table: pen_slots ints
 };
 
 // ---- penalty set: open-addressing hash set of the distinct in-range ids of the window (sampler.cpp:32-38) ------
@@ -131,13 +95,6 @@ __device__ __forceinline__ bool pen_contains(const int *tab, int slots, int id) 
   return false;
 }
 
-// Part 1 (no barrier): clears the table, the filter and the counter.  The caller fetches each thread's first id
-// of the window early, so that the global load is in flight while other work goes on.
-__device__ __forceinline__ void pen_clear(int *tab, int slots, int *unique_ctr, uint32_t *bloom) {
-  for (int i = threadIdx.x; i < slots; i += kThreads) tab[i] = kPenEmpty;
-  for (int i = threadIdx.x; i < kPenBloomBits / 32; i += kThreads) bloom[i] = 0u;
-  if (threadIdx.x == 0) *unique_ctr = 0;
-}
 __device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_total, int *status,
                                           uint32_t *bloom = nullptr) {
   if (t < 0 || t >= vocab_total) return 0;  // out-of-range ids are skipped (sampler.cpp:36)
@@ -153,110 +110,6 @@ __device__ __forceinline__ int pen_insert(int *tab, int slots, int t, int vocab_
   atomicOr(status, ST_PEN_TABLE_FULL);
   return 0;
 }
-// Part 2 (a barrier must separate it from part 1): inserts the window, returns the number of distinct ids.
-__device__ int pen_build(int *tab, int slots, int *unique_ctr, const int *hist, long long from, long long hn,
-                         int first_id, int vocab_total, int *status, uint32_t *bloom) {
-  int mine = pen_insert(tab, slots, first_id, vocab_total, status, bloom);
-  for (long long i = from + kThreads + threadIdx.x; i < hn; i += kThreads)
-    mine += pen_insert(tab, slots, hist[i], vocab_total, status, bloom);
-  if (mine) atomicAdd(unique_ctr, mine);
-  __syncthreads();
-  return *unique_ctr;
-}
-
-// (The block-wide helpers below are called from many places and kept out of line: the cold phases of the kernel are
-// limited by instruction fetch, so code size matters more than call overhead.)
-// ---- radix select over composites ------------------------------------------------------------------------
-// Returns a pivot such that exactly `want` of c[0..n) are >= pivot (composites are distinct).  0 < want < n.
-// 8-bit digits from the top; stops as soon as the chosen bucket is taken whole.  All threads call it.
-__device__ unsigned long long block_select_pivot(const unsigned long long *c, int n, int want, uint32_t *hist,
-                                                 uint32_t *sel) {
-  unsigned long long prefix = 0, mask = 0;
-  uint32_t need = (uint32_t)want;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
-  __syncthreads();
-  for (int shift = 56; shift >= 0; shift -= 8) {
-#pragma unroll 1
-    for (int i = threadIdx.x; i < n; i += kThreads) {
-      const unsigned long long v = c[i];
-      if ((v & mask) == prefix) atomicAdd(&hist[(uint32_t)(v >> shift) & 255u], 1u);
-    }
-    __syncthreads();
-    if (warp == 0) {  // lane l owns bins 8l .. 8l+7: reads them, clears them for the next pass
-      uint32_t loc[8], s = 0;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) { loc[k] = hist[8 * lane + k]; s += loc[k]; hist[8 * lane + k] = 0; }
-      uint32_t suf = s;  // inclusive suffix sum over lanes >= lane
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const uint32_t t = __shfl_down_sync(0xffffffffu, suf, o);
-        if (lane + o < 32) suf += t;
-      }
-      const uint32_t above = suf - s;
-      if (above < need && need <= suf) {
-        uint32_t acc = above;
-#pragma unroll
-        for (int k = 7; k >= 0; --k) {
-          if (acc + loc[k] >= need) { sel[0] = 8 * lane + k; sel[1] = need - acc; sel[2] = loc[k]; break; }
-          acc += loc[k];
-        }
-      }
-    }
-    __syncthreads();
-    const uint32_t d = sel[0], bucket = sel[2];
-    need = sel[1];
-    prefix |= (unsigned long long)d << shift;
-    mask |= 0xffULL << shift;
-    if (need == bucket) break;
-  }
-  return prefix;
-}
-
-// In-place compaction: keeps the entries >= pivot at the front (order not preserved).  Returns the new count.
-__device__ int block_compact(unsigned long long *c, int n, unsigned long long pivot, int *counter) {
-  constexpr int PER = 4;
-  const int lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) *counter = 0;
-  __syncthreads();
-#pragma unroll 1
-  for (int base = 0; base < n; base += PER * kThreads) {
-    unsigned long long r[PER];
-    int mine = 0;
-#pragma unroll
-    for (int k = 0; k < PER; ++k) {
-      const int i = base + k * kThreads + threadIdx.x;
-      r[k] = (i < n) ? c[i] : 0ULL;
-      if (r[k] < pivot) r[k] = 0ULL;  // composites are never 0
-      mine += r[k] != 0ULL;
-    }
-    int incl = mine;  // warp scan of the per-lane keep counts, then one reservation per warp
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += v;
-    }
-    const int total = __shfl_sync(0xffffffffu, incl, 31);
-    __syncthreads();  // every entry of this chunk is in registers before any slot below its end is rewritten
-    int pos = 0;
-    if (lane == 31 && total > 0) pos = atomicAdd(counter, total);
-    pos = __shfl_sync(0xffffffffu, pos, 31) + incl - mine;
-#pragma unroll
-    for (int k = 0; k < PER; ++k)
-      if (r[k] != 0ULL) c[pos++] = r[k];
-  }
-  __syncthreads();
-  return *counter;
-}
-
-// keep the `want` largest of c[0..n) at the front (no-op when n <= want); returns the new count
-__device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int want, uint32_t *hist, uint32_t *sel,
-                                              int *counter) {
-  if (n <= want) return n;
-  const unsigned long long pivot = block_select_pivot(c, n, want, hist, sel);
-  return block_compact(c, n, pivot, counter);
-}
-
 // ---- linear value buckets: a cheap coarse order for short lists -------------------------------------------------
 // 256 equal-width buckets upwards from `lo`.  The mapping is monotone (a larger value never lands in a lower
 // bucket) whatever the inputs, because subtraction, multiplication by a non-negative scale, conversion and
@@ -304,13 +157,163 @@ __device__ __forceinline__ void block_key_range(uint32_t mn, uint32_t mx, uint32
   __syncthreads();
 }
 
+// Everything below is sized by the CTA's thread count NT: a tile is four float4 per thread, the candidate list
+// eight entries per thread.  Two configurations are built: 256 threads (four CTAs per SM; with a deeper ring,
+// fewer) for launches of a few hundred rows at most, where a row's own latency counts, and 128 threads (eight
+// CTAs per SM) for more rows, where more rows in flight per SM even out the compute-only phases.
+// The ring depth is a launch parameter (StreamArgs::log2_stages): stages beyond kMinStages follow the structure in
+// dynamic shared memory, then comes the penalty hash table.
+template <int NT>
+struct Stream {
+  static constexpr int kThreads = NT;
+  static constexpr int kCtasPerSm = 1024 / NT;        // resident CTAs per SM at most (64 registers a thread)
+  static constexpr int kTile = NT * 16;               // floats per ring stage: four float4 per thread
+  static constexpr int kChunk = NT * 4;               // careful mode scans a tile in chunks of one float4 per thread
+  static constexpr int kCandCap = NT * 8;             // candidate entries of the streaming phase
+  static constexpr int kCandHigh = kCandCap - kChunk; // careful mode: select when the list grows beyond this
+  static constexpr int kCandHighFast = NT * 5;        // fast mode: select after a tile that left more than this
+  static constexpr int kRingEntries = kMinStages * kTile * 4 / 8;
+  static constexpr int kMergeCap = kCandCap + kRingEntries;  // entries available to a merge (list + first stages)
+  static constexpr int kMaxCluster = kMergeCap / kSmallMaxM >= 8 ? 8 : 4;  // CTAs whose lists fit the leader's merge
+  static_assert(NT % 32 == 0 && NT >= 128 && NT <= 256, "block size");
+  static_assert(kSmallMaxM <= kCandHigh, "candidate list sizing");
+  static_assert(kMaxCluster * kSmallMaxM <= kMergeCap, "cluster merge sizing");
+  static_assert(kTile % kChunk == 0, "chunking");
+  static_assert(kCandCap >= 1024 && kCandCap * 8 <= kMinStages * kTile * 4, "finish buffers alias list and ring");
+
+struct __align__(128) StreamSmem {
+  uint64_t full[kMaxStages];
+  unsigned long long exp_tab[32];
+  uint32_t hist[256];
+  uint32_t pen_bloom[kPenBloomBits / 32];
+  uint32_t sel[4];
+  int cand_count;
+  int pen_unique;
+  int misc[2];
+  float vbp[2];  // value buckets (lo, scale) of the candidates collected with a guessed threshold
+  alignas(128) unsigned long long cand[kCandCap];  // candidates; the ring follows directly so that a merge can use both
+  alignas(128) float ring[kMinStages][kTile];      // further stages follow the structure
+};
+
+
+// Part 1 (no barrier): clears the table, the filter and the counter.  The caller fetches each thread's first id
+// of the window early, so that the global load is in flight while other work goes on.
+static __device__ __forceinline__ void pen_clear(int *tab, int slots, int *unique_ctr, uint32_t *bloom) {
+  for (int i = threadIdx.x; i < slots; i += kThreads) tab[i] = kPenEmpty;
+  for (int i = threadIdx.x; i < kPenBloomBits / 32; i += kThreads) bloom[i] = 0u;
+  if (threadIdx.x == 0) *unique_ctr = 0;
+}
+// Part 2 (a barrier must separate it from part 1): inserts the window, returns the number of distinct ids.
+static __device__ int pen_build(int *tab, int slots, int *unique_ctr, const int *hist, long long from, long long hn,
+                         int first_id, int vocab_total, int *status, uint32_t *bloom) {
+  int mine = pen_insert(tab, slots, first_id, vocab_total, status, bloom);
+  for (long long i = from + kThreads + threadIdx.x; i < hn; i += kThreads)
+    mine += pen_insert(tab, slots, hist[i], vocab_total, status, bloom);
+  if (mine) atomicAdd(unique_ctr, mine);
+  __syncthreads();
+  return *unique_ctr;
+}
+
+// (The block-wide helpers below are called from many places and kept out of line: the cold phases of the kernel are
+// limited by instruction fetch, so code size matters more than call overhead.)
+// ---- radix select over composites ------------------------------------------------------------------------
+// Returns a pivot such that exactly `want` of c[0..n) are >= pivot (composites are distinct).  0 < want < n.
+// 8-bit digits from the top; stops as soon as the chosen bucket is taken whole.  All threads call it.
+static __device__ unsigned long long block_select_pivot(const unsigned long long *c, int n, int want, uint32_t *hist,
+                                                 uint32_t *sel) {
+  unsigned long long prefix = 0, mask = 0;
+  uint32_t need = (uint32_t)want;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0;
+  __syncthreads();
+  for (int shift = 56; shift >= 0; shift -= 8) {
+#pragma unroll 1
+    for (int i = threadIdx.x; i < n; i += kThreads) {
+      const unsigned long long v = c[i];
+      if ((v & mask) == prefix) atomicAdd(&hist[(uint32_t)(v >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {  // lane l owns bins 8l .. 8l+7: reads them, clears them for the next pass
+      uint32_t loc[8], s = 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { loc[k] = hist[8 * lane + k]; s += loc[k]; hist[8 * lane + k] = 0; }
+      uint32_t suf = s;  // inclusive suffix sum over lanes >= lane
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_down_sync(0xffffffffu, suf, o);
+        if (lane + o < 32) suf += t;
+      }
+      const uint32_t above = suf - s;
+      if (above < need && need <= suf) {
+        uint32_t acc = above;
+#pragma unroll
+        for (int k = 7; k >= 0; --k) {
+          if (acc + loc[k] >= need) { sel[0] = 8 * lane + k; sel[1] = need - acc; sel[2] = loc[k]; break; }
+          acc += loc[k];
+        }
+      }
+    }
+    __syncthreads();
+    const uint32_t d = sel[0], bucket = sel[2];
+    need = sel[1];
+    prefix |= (unsigned long long)d << shift;
+    mask |= 0xffULL << shift;
+    if (need == bucket) break;
+  }
+  return prefix;
+}
+
+// In-place compaction: keeps the entries >= pivot at the front (order not preserved).  Returns the new count.
+static __device__ int block_compact(unsigned long long *c, int n, unsigned long long pivot, int *counter) {
+  constexpr int PER = 4;
+  const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) *counter = 0;
+  __syncthreads();
+#pragma unroll 1
+  for (int base = 0; base < n; base += PER * kThreads) {
+    unsigned long long r[PER];
+    int mine = 0;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int i = base + k * kThreads + threadIdx.x;
+      r[k] = (i < n) ? c[i] : 0ULL;
+      if (r[k] < pivot) r[k] = 0ULL;  // composites are never 0
+      mine += r[k] != 0ULL;
+    }
+    int incl = mine;  // warp scan of the per-lane keep counts, then one reservation per warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    __syncthreads();  // every entry of this chunk is in registers before any slot below its end is rewritten
+    int pos = 0;
+    if (lane == 31 && total > 0) pos = atomicAdd(counter, total);
+    pos = __shfl_sync(0xffffffffu, pos, 31) + incl - mine;
+#pragma unroll
+    for (int k = 0; k < PER; ++k)
+      if (r[k] != 0ULL) c[pos++] = r[k];
+  }
+  __syncthreads();
+  return *counter;
+}
+
+// keep the `want` largest of c[0..n) at the front (no-op when n <= want); returns the new count
+static __device__ __forceinline__ int block_keep_top(unsigned long long *c, int n, int want, uint32_t *hist, uint32_t *sel,
+                                              int *counter) {
+  if (n <= want) return n;
+  const unsigned long long pivot = block_select_pivot(c, n, want, hist, sel);
+  return block_compact(c, n, pivot, counter);
+}
+
 // A value that roughly `r` of the 2 * kThreads sampled maxima (two per thread, m1 >= m2) reach or exceed: the lower
 // edge of the value bucket that holds the r-th largest.  It is a guess (the caller checks what it collects with
 // it); NaN means "no guess" (a flat or non-finite sample).  r <= kThreads.  hist must be zero on entry (it is
 // left zero), sel[0] = 0xffffffff, sel[1] = 0, sel[3] = NaN bits, and a barrier must lie between that set-up and this call.
 // vb_out[0..1] receive the buckets (lo, scale) that the candidates above the guess are later sorted with: from the
 // guess up to as far above the sample's maximum as that lies above the guess.
-__device__ float block_guess_threshold(float m1, float m2, int r, uint32_t *hist, uint32_t *sel, float *vb_out) {
+static __device__ float block_guess_threshold(float m1, float m2, int r, uint32_t *hist, uint32_t *sel, float *vb_out) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t k1 = f2key(m1);
   block_key_range(k1, k1, sel);
@@ -355,8 +358,7 @@ __device__ float block_guess_threshold(float m1, float m2, int r, uint32_t *hist
 // entry is the start of its bucket plus the number of larger composites inside the bucket, which is a short walk
 // unless many entries share a bucket (ties, one huge outlier).  Then nothing is written and -1 comes back, and
 // the caller takes the radix path.  All threads call it.
-constexpr int kBucketWalkMax = 96;
-__device__ int block_top_sorted(const unsigned long long *c, int n, int want, unsigned long long *tmp,
+static __device__ int block_top_sorted(const unsigned long long *c, int n, int want, unsigned long long *tmp,
                                 unsigned long long *out, uint32_t *hist, uint32_t *sel, const float *prepared) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   ValueBuckets vb;
@@ -424,7 +426,7 @@ __device__ int block_top_sorted(const unsigned long long *c, int n, int want, un
 // memory; list and ring are both scratch from here on.  `penalised`: the list already holds penalised values.
 // `prepared`: value buckets (lo, scale) under which S.hist already counts the list's entries, or nullptr.
 // candidate penalty (sampler.cpp:42): positive logits are divided, the others multiplied.  All threads call it.
-__device__ __forceinline__ void penalise_candidates(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
+static __device__ __forceinline__ void penalise_candidates(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
                                                     const uint32_t *bloom, float rp) {
 #pragma unroll 1
   for (int i = threadIdx.x; i < n; i += kThreads) {
@@ -442,7 +444,7 @@ __device__ __forceinline__ void penalise_candidates(unsigned long long *cand, in
 
 // The same in one pass with a count of the (penalised) entries by value bucket (vbp: lo, scale) into hist, which
 // must be zero on entry.
-__device__ __forceinline__ void penalise_and_count(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
+static __device__ __forceinline__ void penalise_and_count(unsigned long long *cand, int n, const int *pen_tab, int pen_slots,
                                                    const uint32_t *bloom, bool any_pen, float rp, const float *vbp,
                                                    uint32_t *hist) {
   ValueBuckets vb;
@@ -463,7 +465,7 @@ __device__ __forceinline__ void penalise_and_count(unsigned long long *cand, int
   __syncthreads();
 }
 
-__device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
+static __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, unsigned long long *cand, int n, int K,
                            const int *pen_tab, int npen, unsigned long long *ring, StreamSmem &S, long long *clk,
                            bool penalised, const float *prepared) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -659,5 +661,10 @@ __device__ void finish_row(const StreamArgs &a, int row, const RowParams &p, uns
     }
   }
 }
+
+  // the kernel body (sample_stream_kernel.cuh)
+  template <int MODE, bool TIMED>
+  static __device__ void run(const StreamArgs &a);
+};  // struct Stream
 
 }  // namespace qpb

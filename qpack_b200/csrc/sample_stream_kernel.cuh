@@ -16,28 +16,31 @@
 
 namespace qpb {
 
-template <int MODE, bool TIMED = false>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+template <int NT>
+template <int MODE, bool TIMED>
+__device__ void Stream<NT>::run(const StreamArgs &a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   StreamSmem &S = *reinterpret_cast<StreamSmem *>(smem_raw);
-  int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem));
+  const int lg = a.log2_stages, nst = 1 << lg;  // ring depth
+  float *const ring = &S.ring[0][0];            // nst stages of kTile floats
+  int *pen_tab = reinterpret_cast<int *>(smem_raw + sizeof(StreamSmem) + (size_t)(nst - kMinStages) * kTile * 4);
 
   cg::cluster_group cluster = cg::this_cluster();
   const int csize = (int)cluster.num_blocks();
   const int crank = (int)cluster.block_rank();
   const int tid = threadIdx.x, lane = tid & 31;
   const int Vt = a.vocab_total;
-  const uint32_t ring_s = smem_u32(&S.ring[0][0]), full_s = smem_u32(&S.full[0]);
+  const uint32_t ring_s = smem_u32(ring), full_s = smem_u32(&S.full[0]);
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) mbar_init(&S.full[s], 1);
+    for (int s = 0; s < nst; ++s) mbar_init(&S.full[s], 1);
     mbar_fence_init();
     S.cand_count = 0;
   }
   if (tid < 32) S.exp_tab[tid] = kExp2Tab[tid];
   __syncthreads();
 
-  int g_next = 0;       // next free ring slot: slot g uses stage g % kStages on phase (g / kStages) & 1
+  int g_next = 0;       // next free ring slot: slot g uses stage g % nst on phase (g / nst) & 1
   bool failed = false;  // a bounded wait on a copy gave up
 
   // ---- one piece: columns [s0, s1) of `row` (local columns of this GPU) ----------------------------------------
@@ -59,25 +62,20 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
     auto issue = [&](int t, int g) {  // thread 0 only: tile t of the piece into ring slot g
       if (t < n_tiles && tile_bulk(t)) {
         const uint32_t bytes = (uint32_t)tile_len(t) * 4u;
-        uint64_t *bar = &S.full[g % kStages];
+        uint64_t *bar = &S.full[g & (nst - 1)];
         mbar_expect_tx(bar, bytes);
-        bulk_g2s(S.ring[g % kStages], rowp + s0 + (size_t)t * kTile, bytes, bar);
+        bulk_g2s(ring + (size_t)(g & (nst - 1)) * kTile, rowp + s0 + (size_t)t * kTile, bytes, bar);
       }
     };
-    // Threshold bootstrap (long pieces only): the first kStages copies fetch tiles spread over the piece as a
+    // Threshold bootstrap (long pieces only): the first kSampleTiles copies fetch tiles spread over the piece as a
     // sample; a value that a chosen number of sampled columns reach becomes the first threshold, so that the
     // stream itself only picks up about twice the columns it needs instead of filling the list several times.
     // It is a guess: if fewer columns pass than are needed, the piece is streamed again without it.
-    const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kStages;
+    const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kSampleTiles;
     int g0 = g_next;  // ring slot of the piece's tile 0 (moved past the sample below)
     if (tid == 0) {
-      for (int j = 0; j < kStages; ++j) issue(can_boot ? (int)((long long)j * n_tiles / kStages) : j, g0 + j);
-      // The ring only holds kStages tiles, so HBM would sit idle while the threshold is worked out: ask for the
-      // next few (full) tiles of the piece to be brought into L2 meanwhile.
-      if (can_boot && kBootPrefetchTiles > 0) {
-        const int np = min(kBootPrefetchTiles, n_tiles - 2);
-        bulk_prefetch_l2(rowp + s0 + kTile, (uint32_t)np * kTile * 4u);
-      }
+      if (can_boot) for (int j = 0; j < kSampleTiles; ++j) issue((int)((long long)j * n_tiles / kSampleTiles), g0 + j);
+      else for (int j = 0; j < nst; ++j) issue(j, g0 + j);
     }
 
     // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
@@ -129,12 +127,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
     bool booted = false;
     if (can_boot) {
       float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
-      for (int j = 0; j < kStages; ++j) {
+      for (int j = 0; j < kSampleTiles; ++j) {
         const int g = g0 + j;
-        if (!mbar_wait_bounded(&S.full[g % kStages], (uint32_t)(g / kStages) & 1u)) failed = true;
+        if (!mbar_wait_bounded(&S.full[g & (nst - 1)], (uint32_t)(g >> lg) & 1u)) failed = true;
 #pragma unroll
         for (int h = 0; h < kTile / (kThreads * 4); ++h) {
-          const float4 v = *reinterpret_cast<const float4 *>(&S.ring[g % kStages][h * kThreads * 4 + tid * 4]);
+          const float4 v = *reinterpret_cast<const float4 *>(ring + (size_t)(g & (nst - 1)) * kTile + h * kThreads * 4 + tid * 4);
           const float f4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -147,12 +145,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
       for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;  // set-up of block_guess_threshold
       if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
       __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
-      g0 += kStages;    // start the stream proper while the threshold is worked out (its tiles are fetched again)
+      g0 += kSampleTiles;  // start the stream proper while the threshold is worked out (its tiles are fetched again)
       if (tid == 0)
-        for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+        for (int j = 0; j < nst; ++j) issue(j, g0 + j);
       if (early_pen) npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
       // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
-      const long long sample = (long long)kStages * kTile;
+      const long long sample = (long long)kSampleTiles * kTile;
       const long long aim = lean ? min((long long)Mloc, (long long)K + 16 + K / 4) : (long long)Mloc;
       long long r = (9LL * aim * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
       r = r < (lean ? kLeanMinRank : 16) ? (lean ? kLeanMinRank : 16) : r;
@@ -199,14 +197,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
       bool careful = false;
       for (int t = 0; t < n_tiles;) {
         const int g = g0 + t;
-        const int st = g % kStages;
+        const int st = g & (nst - 1);
         const int len = tile_len(t);
         const int tbase = s0 + t * kTile;
         if (!careful && thr == thr && len == kTile && base_aligned) {
           // ---- fast tile: full, bulk-copied, threshold known.  Kept to a minimum of instructions: the scan is
           // issue-latency bound with 8 warps per CTA. ----
           const uint32_t bar = full_s + (uint32_t)st * 8u;
-          const uint32_t par = (uint32_t)(g / kStages) & 1u;
+          const uint32_t par = (uint32_t)(g >> lg) & 1u;
           for (int polls = 0; !mbar_try_wait_addr(bar, par);)
             if (++polls > (1 << 22)) { failed = true; break; }
           const int cnt_before = S.cand_count;
@@ -256,17 +254,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
             __syncthreads();
             continue;
           }
-          if (tid == 0) issue(t + kStages, g + kStages);
+          if (tid == 0) issue(t + nst, g + nst);
           if (cnt > kCandHighFast && cnt > Mloc) shrink();
           ++t;
           continue;
         }
         // ---- general tile: ragged, unaligned, no threshold yet, or careful mode ----
         if (tile_bulk(t)) {
-          if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g / kStages) & 1u)) failed = true;
+          if (!mbar_wait_bounded(&S.full[st], (uint32_t)(g >> lg) & 1u)) failed = true;
         } else {  // unaligned row or ragged tail: plain loads into the same stage
 #pragma unroll 1
-          for (int i = tid; i < len; i += kThreads) S.ring[st][i] = rowp[tbase + i];
+          for (int i = tid; i < len; i += kThreads) (ring + (size_t)st * kTile)[i] = rowp[tbase + i];
           if (tid == 0) mbar_arrive(&S.full[st]);  // nobody waits on it, but the slot's phase has to advance
           __syncthreads();
         }
@@ -276,7 +274,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
         for (int q = 0; q < kTile / kChunk; ++q) {
           const int qlen = min(kChunk, len - q * kChunk);  // columns of this chunk (uniform)
           if (qlen <= 0) break;
-          const float *src = &S.ring[st][q * kChunk];
+          const float *src = &(ring + (size_t)st * kTile)[q * kChunk];
           const float4 v = smem_load_f4(src + tid * 4);
           const float f[4] = {v.x, v.y, v.z, v.w};
           const int qbase = a.id_offset + tbase + q * kChunk;  // global id of the chunk's first column
@@ -340,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
           __syncthreads();
           continue;
         }
-        if (tid == 0) issue(t + kStages, g + kStages);
+        if (tid == 0) issue(t + nst, g + nst);
         if (!slow && cnt > kCandHighFast && cnt > Mloc) shrink();
         ++t;
       }
@@ -438,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
       thr = __int_as_float(0x7fc00000);
       if (tid == 0) {
         S.cand_count = 0;
-        for (int j = 0; j < kStages; ++j) issue(j, g0 + j);
+        for (int j = 0; j < nst; ++j) issue(j, g0 + j);
       }
       if (clk) clk[14] += 1;
       __syncthreads();
@@ -541,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
     // raw cut can be skipped; a penalty below 1 raises values and needs it.
     if (npen > 0 && !(p.repeat_penalty >= 1.f)) n = block_keep_top(S.cand, n, M, S.hist, S.sel, &S.cand_count);
 
-    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, reinterpret_cast<unsigned long long *>(&S.ring[0][0]), S, clk, penalised,
+    finish_row(a, row, p, S.cand, n, K, pen_tab, npen, reinterpret_cast<unsigned long long *>(ring), S, clk, penalised,
                (hist_ok && penalised) ? S.vbp : nullptr);
     QPB_STAMP(7);
     __syncthreads();  // the ring (sorted) and the list are free for the next piece
@@ -582,6 +580,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) stream_rows_kernel(const
     }
     do_piece(row, s0, s1, npieces, pi, clk);
   }
+}
+
+template <int NT, int MODE, bool TIMED = false>
+__global__ void __launch_bounds__(NT, 1024 / NT) stream_rows_kernel(const __grid_constant__ StreamArgs a) {
+  Stream<NT>::template run<MODE, TIMED>(a);
 }
 
 }  // namespace qpb

@@ -34,8 +34,9 @@ struct qpb_sampler {
   int routed_rows = -1, routed_vocab = -1, n_stream = 0, n_whole = 0, max_window = 0;
   long long routed_hist_cap = -1;
   int cluster = 0;
-  int stream_slots = 0;  // CTAs of the streaming kernel resident on the GPU at once (0: not queried yet)
-  bool attr_done[6] = {false, false, false, false, false, false};
+  bool attr_done[2][3][2] = {};  // streaming kernel instantiations: [block size][mode][timed]
+  bool whole_attr_done = false;
+  int force_threads = 0, force_log2_stages = 0;  // 0: chosen per launch
   int64_t launches = 0;
   // staging for the host-buffer entry point
   float *d_stage_logits = nullptr;
@@ -129,25 +130,53 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
   return QPB_OK;
 }
 
+// Block size and ring depth of a streaming launch, by the CTAs it puts in flight: up to four per SM run with 256
+// threads (a row's own latency counts: a ring as deep as the SM's shared memory allows for the CTAs it hosts),
+// more run with 128 threads, eight to an SM.
+struct StreamPlan {
+  int nt, lg;
+};
+size_t stream_smem(const StreamPlan &pl, int pen_slots) {
+  const size_t base = pl.nt == 128 ? sizeof(Stream<128>::StreamSmem) : sizeof(Stream<256>::StreamSmem);
+  return base + (size_t)((1 << pl.lg) - kMinStages) * (size_t)pl.nt * 16 * 4 + (size_t)pen_slots * sizeof(int);
+}
+constexpr size_t kSmemLimit = 227 * 1024;
+StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots) {
+  StreamPlan pl;
+  pl.nt = s->force_threads ? s->force_threads : (ctas > 4LL * s->sm_count ? 128 : 256);
+  if (s->force_log2_stages) pl.lg = s->force_log2_stages;
+  else if (pl.nt == 128) pl.lg = 1;
+  else pl.lg = ctas <= s->sm_count ? 3 : (ctas <= 2LL * s->sm_count ? 2 : 1);
+  while (pl.lg > 1 && stream_smem(pl, pen_slots) > kSmemLimit) pl.lg--;
+  return pl;
+}
+int max_cluster(int nt) { return nt == 128 ? Stream<128>::kMaxCluster : Stream<256>::kMaxCluster; }
+int merge_cap(int nt) { return nt == 128 ? Stream<128>::kMergeCap : Stream<256>::kMergeCap; }
+
 int pick_cluster(const qpb_sampler *s, int rows) {
-  if (s->cluster) return s->cluster < kMaxStreamCluster ? s->cluster : kMaxStreamCluster;
-  // one CTA per row as soon as a handful of rows are in flight; a cluster only pays for a few rows
-  return rows <= 8 ? kMaxStreamCluster : 1;
+  // A single CTA takes a few tens of microseconds over a row, so while SMs are to spare a row is split over a
+  // cluster: as wide as keeps the launch at or below three CTAs per SM.
+  int c = s->cluster;
+  if (!c) c = 4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 3LL * s->sm_count ? 2 : 1);
+  const int nt = plan_stream(s, (long long)rows * c, 64).nt;
+  return c < max_cluster(nt) ? c : max_cluster(nt);
 }
 
 template <int MODE>
-int launch_stream(qpb_sampler *s, const StreamArgs &args, int ctas, int cluster, cudaStream_t st);
+int launch_stream(qpb_sampler *s, const StreamArgs &args, int ctas, int cluster, cudaStream_t st, int nt = 0);
 
 // Cuts the rows of a launch into persistent pieces when that pays: fills the piece fields of `a` and returns the
-// number of CTAs to launch (0: keep one row per CTA / cluster).
-int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas) {
+// number of CTAs to launch (0: keep one row per CTA / cluster) and the block size the tiles were counted for.
+int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas, int *nt_out) {
   *ctas = 0;
   if (s->pieces < 0 || s->cluster || s->d_phase_clk || n_rows < 2) return QPB_OK;
-  const int slots = s->stream_slots > 0 ? s->stream_slots : 4 * s->sm_count;
+  const int nt = plan_stream(s, n_rows, a.pen_slots).nt;
+  const int slots = (1024 / nt) * s->sm_count;
   // Pieces cost a threshold bootstrap, a cut and a trip through scratch each, so whole rows win unless their last
   // wave would leave most of the GPU idle.
   if (s->pieces == 0 && (n_rows <= slots || (n_rows % slots) * 4 > slots || n_rows % slots == 0)) return QPB_OK;
-  const long long tpr = (a.vocab + kTile - 1) / kTile;
+  const int tile = nt * 16;
+  const long long tpr = (a.vocab + tile - 1) / tile;
   const long long total = (long long)n_rows * tpr;
   const long long min_units = 12;  // shorter pieces cannot bootstrap a threshold
   if (tpr < min_units) return QPB_OK;
@@ -156,7 +185,7 @@ int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas) {
   const long long Q = (total + G - 1) / G;
   G = (total + Q - 1) / Q;
   const int max_pieces = (int)((tpr + Q - 1) / Q) + 1;
-  if ((long long)max_pieces * kSmallMaxM > kMergeCap) return QPB_OK;
+  if ((long long)max_pieces * kSmallMaxM > merge_cap(nt)) return QPB_OK;
   if (max_pieces > s->piece_cap) {
     QPB_CUDA(s, cudaDeviceSynchronize());
     cudaFree(s->d_piece_cand);
@@ -178,25 +207,22 @@ int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas) {
   a.piece_cnt = s->d_piece_cnt;
   a.piece_done = s->d_piece_done;
   *ctas = (int)G;
+  *nt_out = nt;
   return QPB_OK;
 }
 
-template <int MODE>
-int launch_stream(qpb_sampler *s, const StreamArgs &args, int rows, int cluster, cudaStream_t st) {
-  const size_t smem = sizeof(StreamSmem) + (size_t)args.pen_slots * sizeof(int);
-  if (smem > 200 * 1024) return fail(s, QPB_ERR_UNSUPPORTED, "history window too large for the penalty table");
-  if (!s->attr_done[MODE]) {  // once per handle (the attribute is per device)
-    QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    s->attr_done[MODE] = true;
-    if (MODE == MODE_SAMPLE) {
-      int per_sm = 0;
-      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, stream_rows_kernel<MODE>, kThreads, smem) == cudaSuccess && per_sm > 0)
-        s->stream_slots = per_sm * s->sm_count;
-    }
+template <int NT, int MODE>
+int launch_stream_nt(qpb_sampler *s, const StreamArgs &args, int rows, int cluster, size_t smem, cudaStream_t st) {
+  const bool timed = MODE == MODE_SAMPLE && args.phase_clk != nullptr;
+  bool &done = s->attr_done[NT == 128 ? 0 : 1][MODE][timed ? 1 : 0];
+  if (!done) {  // once per handle (the attribute is per device)
+    if (timed) QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<NT, MODE_SAMPLE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
+    else QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<NT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));
+    done = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(rows * cluster), 1, 1);
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(NT, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -206,17 +232,26 @@ int launch_stream(qpb_sampler *s, const StreamArgs &args, int rows, int cluster,
   at[0].val.clusterDim.z = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  if (MODE == MODE_SAMPLE && args.phase_clk) {
-    if (!s->attr_done[2 + MODE_MERGE]) {
-      QPB_CUDA(s, cudaFuncSetAttribute(stream_rows_kernel<MODE_SAMPLE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      s->attr_done[2 + MODE_MERGE] = true;
-    }
-    QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<MODE_SAMPLE, true>, args));
-  } else {
-    QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<MODE>, args));
-  }
+  if (timed) QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<NT, MODE_SAMPLE, true>, args));
+  else QPB_CUDA(s, cudaLaunchKernelEx(&cfg, stream_rows_kernel<NT, MODE>, args));
   s->launches++;
   return QPB_OK;
+}
+
+template <int MODE>
+int launch_stream(qpb_sampler *s, const StreamArgs &args_in, int rows, int cluster, cudaStream_t st, int nt) {
+  StreamArgs args = args_in;
+  StreamPlan pl = plan_stream(s, (long long)rows * cluster, args.pen_slots);
+  if (nt) {  // the caller counted tiles for this block size
+    pl.nt = nt;
+    if (nt == 128) pl.lg = 1;
+  }
+  if (cluster > max_cluster(pl.nt)) return fail(s, QPB_ERR_INVALID, "cluster too large for the block size");
+  args.log2_stages = pl.lg;
+  const size_t smem = stream_smem(pl, args.pen_slots);
+  if (smem > kSmemLimit) return fail(s, QPB_ERR_UNSUPPORTED, "history window too large for the penalty table");
+  if (pl.nt == 128) return launch_stream_nt<128, MODE>(s, args, rows, cluster, smem, st);
+  return launch_stream_nt<256, MODE>(s, args, rows, cluster, smem, st);
 }
 
 struct Inputs {
@@ -288,9 +323,9 @@ int launch_whole(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d
     return fail(s, QPB_ERR_UNSUPPORTED, "vocabulary too large for the whole-row kernel (about 440k columns)");
   wa.have_e = fixed + (size_t)per * 8 <= limit ? 1 : 0;
   const size_t smem = fixed + (size_t)per * (wa.have_e ? 8 : 4);
-  if (!s->attr_done[3]) {
+  if (!s->whole_attr_done) {
     QPB_CUDA(s, cudaFuncSetAttribute(whole_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
-    s->attr_done[3] = true;
+    s->whole_attr_done = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(s->n_whole * cluster), 1, 1);
@@ -329,10 +364,10 @@ int run_rows(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dis
     a.max_out = max_out;
     a.n_rows = s->n_stream;
     a.row_list = s->d_rows_stream;
-    int ctas = 0;
-    rc = plan_pieces(s, a, s->n_stream, &ctas);
+    int ctas = 0, nt = 0;
+    rc = plan_pieces(s, a, s->n_stream, &ctas, &nt);
     if (rc) return rc;
-    if (ctas > 0) rc = launch_stream<MODE_SAMPLE>(s, a, ctas, 1, st);
+    if (ctas > 0) rc = launch_stream<MODE_SAMPLE>(s, a, ctas, 1, st, nt);
     else rc = launch_stream<MODE_SAMPLE>(s, a, s->n_stream, pick_cluster(s, s->n_stream), st);
     if (rc) return rc;
   }
@@ -589,6 +624,15 @@ int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state313) {
   return QPB_OK;
 }
 
+int qpb_sampler_set_stream_config(qpb_sampler *s, int threads, int log2_stages) {
+  if (!s) return QPB_ERR_INVALID;
+  if ((threads != 0 && threads != 128 && threads != 256) || log2_stages < 0 || log2_stages > 3)
+    return fail(s, QPB_ERR_INVALID, "threads must be 0, 128 or 256 and log2_stages 0..3");
+  s->force_threads = threads;
+  s->force_log2_stages = log2_stages;
+  return QPB_OK;
+}
+
 int qpb_sampler_set_cluster(qpb_sampler *s, int cluster) {
   if (!s) return QPB_ERR_INVALID;
   if (cluster < 0 || cluster > 8) return fail(s, QPB_ERR_INVALID, "cluster must be 0 (automatic) or 1..8");
@@ -662,7 +706,7 @@ int qpb_sampler_local_candidates(qpb_sampler *s, const float *d_logits, int64_t 
   a.cand_io = reinterpret_cast<unsigned long long *>(d_cand);
   a.cand_slots = slots;
   a.cand_rows = n_rows;
-  return launch_stream<MODE_LOCAL_TOPM>(s, a, n_rows, pick_cluster(s, n_rows), (cudaStream_t)stream);
+  return launch_stream<MODE_LOCAL_TOPM>(s, a, n_rows, 1, (cudaStream_t)stream);  // one CTA per row and shard
 }
 
 int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_shards, int n_rows, int slots,
@@ -671,7 +715,7 @@ int qpb_sampler_merge_sample(qpb_sampler *s, const uint64_t *d_cand_all, int n_s
                              int32_t *d_dist_count, int max_out, int32_t *d_out_ids, void *stream) {
   if (!s) return QPB_ERR_INVALID;
   if (!d_cand_all || n_shards <= 0 || slots <= 0) return fail(s, QPB_ERR_INVALID, "candidate buffer invalid");
-  if ((long long)n_shards * slots > kMergeCap) return fail(s, QPB_ERR_UNSUPPORTED, "n_shards * slots exceeds the merge list");
+  if ((long long)n_shards * slots > merge_cap(plan_stream(s, n_rows, 64).nt)) return fail(s, QPB_ERR_UNSUPPORTED, "n_shards * slots exceeds the merge list");
   if (!d_out_ids && !d_dist_count) return fail(s, QPB_ERR_INVALID, "no output requested");
   Inputs in{nullptr, 0, n_rows, vocab_total, vocab_total, 0, d_history, hist_stride, d_hist_len, hist_len_all};
   int rc = check_inputs(s, in, false);
@@ -790,7 +834,7 @@ int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, con
       void *ptr = nullptr;
       cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
       if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(stream_rows_kernel<MODE_SAMPLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        e = cudaFuncSetAttribute(stream_rows_kernel<256, MODE_SAMPLE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit);
       if (e != cudaSuccess || !ptr) {
         static_msg(errbuf, errbuf_len, cudaGetErrorString(e));
         return QPB_ERR_CUDA;
@@ -831,12 +875,16 @@ int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, con
   a.draw = 1;
   a.pen_slots = pen_slots_for(max_window);
   a.status = d_status ? d_status : d_stat;
-  const size_t smem = sizeof(StreamSmem) + (size_t)a.pen_slots * sizeof(int);
-  if (smem > 200 * 1024) {
+  // at most QPB_STATIC_MAX_ROWS CTAs, one per row: 256 threads, the deepest ring that leaves room for the table
+  StreamPlan pl = {256, 3};
+  while (pl.lg > 1 && stream_smem(pl, a.pen_slots) > kSmemLimit) pl.lg--;
+  const size_t smem = stream_smem(pl, a.pen_slots);
+  if (smem > kSmemLimit) {
     static_msg(errbuf, errbuf_len, "history window too large for the penalty table");
     return QPB_ERR_UNSUPPORTED;
   }
-  stream_rows_kernel<MODE_SAMPLE><<<n_rows, kThreads, smem, st>>>(a);
+  a.log2_stages = pl.lg;
+  stream_rows_kernel<256, MODE_SAMPLE><<<n_rows, 256, smem, st>>>(a);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     static_msg(errbuf, errbuf_len, cudaGetErrorString(e));

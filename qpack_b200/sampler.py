@@ -79,6 +79,10 @@ class BatchSampler:
         params = np.ascontiguousarray(params, dtype=PARAMS_DTYPE)
         self._ck(self._lib.qpb_sampler_set_params(self._h, params.ctypes.data, int(params.shape[0])))
 
+    def set_stream_config(self, threads: int = 0, log2_stages: int = 0):
+        """Threads per CTA (128 / 256) and log2 ring depth (1..3) of the streaming kernel; 0 = chosen per launch."""
+        self._ck(self._lib.qpb_sampler_set_stream_config(self._h, int(threads), int(log2_stages)))
+
     def set_cluster(self, cluster: int):
         self._ck(self._lib.qpb_sampler_set_cluster(self._h, int(cluster)))
 

@@ -15,11 +15,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def run_device(params, logits, hist=None, hist_len=None, max_out=64, cluster=0, draw=True):
+def run_device(params, logits, hist=None, hist_len=None, max_out=64, cluster=0, draw=True, config=(0, 0)):
     B = logits.shape[0]
     bs = BatchSampler(B, 0)
     bs.set_params(params)
     bs.set_cluster(cluster)
+    bs.set_stream_config(*config)
     d_logits = torch.from_numpy(np.ascontiguousarray(logits)).to(DEV)
     d_hist = torch.from_numpy(np.ascontiguousarray(hist)).to(DEV) if hist is not None else None
     d_hl = torch.from_numpy(np.ascontiguousarray(hist_len)).to(DEV) if hist_len is not None else None
@@ -135,6 +136,19 @@ def test_config_rows(name, rows, cluster):
     assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, rep
 
 
+@pytest.mark.parametrize("config", [(128, 1), (128, 2), (256, 1), (256, 2), (256, 3)])
+@pytest.mark.parametrize("name", ["serving", "mixed"])
+def test_block_sizes_and_ring_depths(name, config):
+    """Every build of the streaming kernel (threads per CTA, ring depth) gives the reference's results."""
+    wl = {"serving": synth.serving_batch, "mixed": synth.mixed_batch}[name](rows=40)
+    wl.params["top_k"][wl.params["top_k"] == 0] = 200  # keep every row on the streaming kernel
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    for cluster in (1, 4):
+        got = run_device(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64, cluster=cluster, config=config)
+        rep = compare_rows(*got, exp)
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (cluster, rep)
+
+
 @pytest.mark.parametrize("rows", [7, 96, 700])
 def test_rows_in_pieces(rows):
     """Row pieces forced on: rows straddle CTAs, piece winners meet in device scratch, the last arriver finishes.
@@ -174,10 +188,11 @@ def test_unaligned_rows_take_the_plain_load_path():
     bs.close()
 
 
-def test_vocab_sharded_emulated_on_one_gpu():
+@pytest.mark.parametrize("rows", [3, 32])
+def test_vocab_sharded_emulated_on_one_gpu(rows):
     """Config 5 on one GPU: the G column shards are processed one after the other, their candidate lists
     stacked as an all-gather would, then merged; ids equal the checker on the whole row."""
-    wl = synth.sharded_batch(rows=32)
+    wl = synth.sharded_batch(rows=rows)
     exp = Oracle.sample_rows(wl.params, wl.logits, None, None, max_out=64)
     B, V = wl.logits.shape
     d_x = torch.from_numpy(wl.logits).to(DEV)
