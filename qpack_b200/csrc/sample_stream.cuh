@@ -26,7 +26,8 @@ namespace cg = cooperative_groups;
 // quarter of the vocabulary (top_m then returns the whole row, sampler.cpp:14): the host routes them away.
 constexpr int kSmallMaxM = 500;
 constexpr int kLeanMinRank = 12;      // lowest sample rank a lean threshold is taken at
-constexpr int kSampleTiles = 2;       // tiles fetched ahead of the stream to guess a threshold from
+constexpr int kSampleTiles = 2;       // ring stages filled with a sample of the row to guess a threshold from
+constexpr int kSampleChunks = 8;      // evenly spaced runs of columns per sample stage
 constexpr int kMinStages = 2;         // ring stages every configuration has (the merge and the finish reuse them)
 constexpr int kMaxStages = 8;         // deepest ring (a power of two, like every ring depth)
 constexpr int kPenBloomBits = 4096;   // one-probe negative test in front of the penalty hash table

@@ -67,17 +67,35 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
         bulk_g2s(ring + (size_t)(g & (nst - 1)) * kTile, rowp + s0 + (size_t)t * kTile, bytes, bar);
       }
     };
-    // Threshold bootstrap (long pieces only): the first kSampleTiles copies fetch tiles spread over the piece as a
-    // sample; a value that a chosen number of sampled columns reach becomes the first threshold, so that the
-    // stream itself only picks up about twice the columns it needs instead of filling the list several times.
-    // It is a guess: if fewer columns pass than are needed, the piece is streamed again without it.
+    // Threshold bootstrap (long pieces only): the first kSampleTiles stages are filled with a sample of the piece;
+    // a value that a chosen number of sampled columns reach becomes the first threshold, so that the stream itself
+    // only picks up about twice the columns it needs instead of filling the list several times.  It is a guess: if
+    // fewer columns pass than are needed, the piece is streamed again without it.  The sample is kSampleChunks
+    // short runs per stage, evenly spaced over the piece (logits correlate with the token id: frequent tokens sit
+    // at low ids), one bulk copy each, issued by as many threads.
     const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kSampleTiles;
     int g0 = g_next;  // ring slot of the piece's tile 0 (moved past the sample below)
-    if (tid == 0) {
-      if (can_boot) for (int j = 0; j < kSampleTiles; ++j) issue((int)((long long)j * n_tiles / kSampleTiles), g0 + j);
-      else for (int j = 0; j < nst; ++j) issue(j, g0 + j);
+    if (can_boot) {
+      constexpr int kRuns = kSampleTiles * kSampleChunks, kRunLen = kTile / kSampleChunks;  // floats per run
+      if (tid < kRuns) {
+        const int j = tid / kSampleChunks, g = g0 + j;
+        const long long span = ((long long)(s1 - s0) & ~3LL) - kRunLen;  // first column of the last run
+        const long long pos = ((span * tid) / (kRuns - 1)) & ~3LL;       // 16-byte steps from an aligned base
+        uint64_t *bar = &S.full[g & (nst - 1)];
+        if (tid % kSampleChunks == 0) mbar_expect_tx(bar, kTile * 4u);
+        bulk_g2s(ring + (size_t)(g & (nst - 1)) * kTile + (tid % kSampleChunks) * kRunLen, rowp + s0 + pos, kRunLen * 4u, bar);
+      }
+    } else if (tid == 0) {
+      for (int j = 0; j < nst; ++j) issue(j, g0 + j);
     }
 
+    // The window's ids can only be loaded once the row's parameters and history length have arrived; with HBM
+    // saturated by the other CTAs' streams that second trip costs microseconds, so the history row is asked into
+    // L2 right away (one line per thread, the tail of the row first: the window is its end).
+    if (a.history != nullptr && crank == 0) {
+      const long long lines = (a.hist_stride * 4 + 127) / 128;
+      if (tid < lines) prefetch_l2(reinterpret_cast<const char *>(a.history + (size_t)row * a.hist_stride) + (lines - 1 - tid) * 128);
+    }
     // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
     // (the RNG words are only pulled towards L2 here: holding them in registers through the scan costs occupancy)
     if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw) {

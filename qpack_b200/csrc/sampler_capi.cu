@@ -131,8 +131,7 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
 }
 
 // Block size and ring depth of a streaming launch, by the CTAs it puts in flight: up to four per SM run with 256
-// threads (a row's own latency counts: a ring as deep as the SM's shared memory allows for the CTAs it hosts),
-// more run with 128 threads, eight to an SM.
+// threads (a row's own latency counts), more run with 128 threads, eight to an SM.
 struct StreamPlan {
   int nt, lg;
 };
@@ -145,8 +144,7 @@ StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots) {
   StreamPlan pl;
   pl.nt = s->force_threads ? s->force_threads : (ctas > 4LL * s->sm_count ? 128 : 256);
   if (s->force_log2_stages) pl.lg = s->force_log2_stages;
-  else if (pl.nt == 128) pl.lg = 1;
-  else pl.lg = ctas <= s->sm_count ? 3 : (ctas <= 2LL * s->sm_count ? 2 : 1);
+  else pl.lg = 1;  // deeper rings measured no faster: one CTA is bound by its own scan, many CTAs by HBM
   while (pl.lg > 1 && stream_smem(pl, pen_slots) > kSmemLimit) pl.lg--;
   return pl;
 }
@@ -363,7 +361,7 @@ int run_rows(qpb_sampler *s, const Inputs &in, int32_t *d_dist_ids, float *d_dis
     a.dist_count = d_dist_count;
     a.max_out = max_out;
     a.n_rows = s->n_stream;
-    a.row_list = s->d_rows_stream;
+    a.row_list = s->n_whole > 0 ? s->d_rows_stream : nullptr;  // every row here: no indirection to wait for
     int ctas = 0, nt = 0;
     rc = plan_pieces(s, a, s->n_stream, &ctas, &nt);
     if (rc) return rc;
@@ -875,9 +873,8 @@ int qpb_sample_rows_static(const qpb_sampler_params *h_params, int n_params, con
   a.draw = 1;
   a.pen_slots = pen_slots_for(max_window);
   a.status = d_status ? d_status : d_stat;
-  // at most QPB_STATIC_MAX_ROWS CTAs, one per row: 256 threads, the deepest ring that leaves room for the table
-  StreamPlan pl = {256, 3};
-  while (pl.lg > 1 && stream_smem(pl, a.pen_slots) > kSmemLimit) pl.lg--;
+  // at most QPB_STATIC_MAX_ROWS CTAs, one per row: 256 threads
+  StreamPlan pl = {256, 1};
   const size_t smem = stream_smem(pl, a.pen_slots);
   if (smem > kSmemLimit) {
     static_msg(errbuf, errbuf_len, "history window too large for the penalty table");
