@@ -46,3 +46,35 @@ def compare_rows(got_ids, got_cnt, got_dids, got_dp, exp, uniforms=None, ordered
     assert rep["count_diff"] == 0, rep
     assert rep["max_dp"] <= P_TOL, rep
     return rep
+
+
+def adversarial_rows(V, rng):
+    """Rows that defeat a sampled threshold or crowd the value buckets: orderings, plateaus, ties, outliers."""
+    base = rng.standard_normal(V).astype(np.float32) * 2.0
+    rows = {}
+    rows["ascending"] = np.sort(base)
+    rows["descending"] = np.sort(base)[::-1].copy()
+    rows["constant"] = np.full(V, 1.25, np.float32)
+    two = np.where(rng.random(V) < 0.01, 3.0, -1.0).astype(np.float32)
+    rows["two_values"] = two
+    head = base.copy()
+    head[:3000] += 9.0  # everything that matters sits at low ids
+    rows["head_heavy"] = head
+    tail = base.copy()
+    tail[-700:] += 9.0
+    rows["tail_heavy"] = tail
+    outl = base.copy()
+    outl[77777] = 3.0e38
+    rows["huge_outlier"] = outl
+    neg = -np.abs(base) - 1.0
+    neg[rng.integers(0, V, 64)] = -1e-3  # log-probability-like: all negative, the best ones next to zero
+    rows["negative"] = neg.astype(np.float32)
+    minf = base.copy()
+    minf[rng.random(V) < 0.9] = -np.inf
+    rows["mostly_minus_inf"] = minf
+    quant = np.round(base * 4.0) / 4.0  # heavy ties across the whole range
+    rows["quantised"] = quant.astype(np.float32)
+    plateau = base.copy()
+    plateau[rng.integers(0, V, 5000)] = 6.0  # thousands of equal maxima: the K best are decided by index
+    rows["plateau"] = plateau
+    return rows

@@ -9,7 +9,7 @@ from oracle import Oracle, make_params
 from qpack_b200 import synth
 from qpack_b200.sampler import BatchSampler, SamplerError, device_expf
 
-from helpers import compare_rows, small_case
+from helpers import adversarial_rows, compare_rows, small_case
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -147,6 +147,28 @@ def test_block_sizes_and_ring_depths(name, config):
         got = run_device(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64, cluster=cluster, config=config)
         rep = compare_rows(*got, exp)
         assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (cluster, rep)
+
+
+@pytest.mark.parametrize("config", [(0, 0), (128, 1)])
+def test_adversarial_rows(config):
+    """Full-vocabulary rows on which the threshold guess fails, the list overflows or one value bucket holds most
+    candidates: the fallback paths must give the checker's result."""
+    V = 151936
+    rng = np.random.default_rng(7)
+    rows = adversarial_rows(V, rng)
+    names = list(rows)
+    logits = np.stack([rows[n] for n in names]).astype(np.float32)
+    B = len(names)
+    hist = rng.integers(0, V, (B, 96)).astype(np.int32)
+    hist[:, :8] = np.argsort(-logits, axis=1, kind="stable")[:, :8]  # some of the best ids are penalised
+    for top_k, rp in ((50, 1.15), (200, 1.0), (40, 0.9), (1, 1.3)):
+        params = synth.make_params(B, temperature=0.8, top_k=top_k, top_p=0.95, min_p=0.01, repeat_penalty=rp,
+                                   repeat_last_n=96, seed=np.arange(B) + 11)
+        exp = Oracle.sample_rows(params, logits, hist, None, max_out=256)
+        for cluster in (1, 4):
+            got = run_device(params, logits, hist, None, max_out=256, cluster=cluster, config=config)
+            rep = compare_rows(*got, exp)
+            assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (top_k, rp, cluster, rep)
 
 
 @pytest.mark.parametrize("rows", [7, 96, 700])

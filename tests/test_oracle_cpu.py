@@ -111,3 +111,26 @@ def test_random_rows_against_compiled_reference():
         for k in ("ids", "count", "dist_ids"):
             assert np.array_equal(a[k], b[k]), (case, k)
         assert np.array_equal(a["dist_p"].view(np.uint32), b["dist_p"].view(np.uint32)), case
+
+
+def test_adversarial_rows_against_compiled_reference():
+    """The rows the GPU tests use to force the fallback paths (orderings, plateaus, ties, outliers, -inf): the
+    checker agrees with the compiled reference on them, so they are valid expectations."""
+    if not Ref.available():
+        pytest.skip("compiled reference not present")
+    from helpers import adversarial_rows
+    V = 151936
+    rng = np.random.default_rng(7)
+    rows = adversarial_rows(V, rng)
+    x = np.stack([rows[n] for n in rows]).astype(np.float32)
+    B = x.shape[0]
+    hist = rng.integers(0, V, (B, 96)).astype(np.int32)
+    hist[:, :8] = np.argsort(-x, axis=1, kind="stable")[:, :8]
+    for top_k, rp in ((50, 1.15), (200, 1.0), (40, 0.9), (1, 1.3)):
+        p = make_params(B, temperature=0.8, top_k=top_k, top_p=0.95, min_p=0.01, repeat_penalty=rp, repeat_last_n=96,
+                        seed=np.arange(B) + 11)
+        a = Oracle.sample_rows(p, x, hist, None, max_out=256)
+        b = Ref.sample_rows(p, x, hist, None, max_out=256, threads=2)
+        for k in ("ids", "count", "dist_ids"):
+            assert np.array_equal(a[k], b[k]), (top_k, rp, k)
+        assert np.array_equal(a["dist_p"].view(np.uint32), b["dist_p"].view(np.uint32)), (top_k, rp)
