@@ -143,8 +143,9 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     // kernels_x86.cpp:509).  A NaN logit passes the test and is ordered below -inf by its key later.
     float thr = __int_as_float(0x7fc00000);
     bool booted = false;
+    float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
+    int second_rank = 0;                             // rank of a second, lower guess should the first one fail
     if (can_boot) {
-      float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
       for (int j = 0; j < kSampleTiles; ++j) {
         const int g = g0 + j;
         if (!mbar_wait_bounded(&S.full[g & (nst - 1)], (uint32_t)(g >> lg) & 1u)) failed = true;
@@ -177,6 +178,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
         thr = block_guess_threshold(m1, m2, (int)r, S.hist, S.sel, S.vbp);  // NaN: no usable guess
         booted = thr == thr;
         have_vb = booted;
+        if (booted && 4 * r + 16 <= kThreads * 3 / 4) second_rank = (int)(4 * r + 16);
       }
     }
     QPB_STAMP(1);
@@ -452,6 +454,16 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       __syncthreads();
       booted = have_vb = hist_ok = false;
       thr = __int_as_float(0x7fc00000);
+      if (second_rank > 0) {
+        // The sample misled the first guess (sorted or clustered logits).  Before the exact stream, which can cost
+        // a select per chunk on such data, one more try with a threshold well down the sample.
+        for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;
+        if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
+        __syncthreads();
+        thr = block_guess_threshold(m1, m2, second_rank, S.hist, S.sel, S.vbp);
+        booted = have_vb = thr == thr;
+        second_rank = 0;
+      }
       if (tid == 0) {
         S.cand_count = 0;
         for (int j = 0; j < nst; ++j) issue(j, g0 + j);
