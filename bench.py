@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 VOCAB = 151936
-NCU_DRAM_BYTES_PER_ROW = 631_360  # (183.41 MB read + 3.47 MB written) / 296 rows; algorithmic: 4 * V = 607_744
+NCU_DRAM_BYTES_PER_ROW = 624_500  # (365.62 MB read + 4.08 MB written) / 592 rows, 128-thread build; algorithmic: 4 * V = 607_744
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
 
@@ -279,7 +279,7 @@ def run_ours(args, rank, world, local_rank):
         bytes_per_launch = rows * 4 * VOCAB
         achieved = bytes_per_launch / (ms * 1e-3) / 1e9
         # DRAM bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel on a
-        # 296-row case of the same workload (profiles/stream_rows_kernel_serving_batch.md), scaled by rows
+        # 592-row case of the same workload (profiles/stream_rows_kernel_serving_batch.md), scaled by rows
         traffic = NCU_DRAM_BYTES_PER_ROW * rows
         line = {
             "metric": "rows sampled/sec at V=151936", "value": rows * world / (ms * 1e-3), "unit": "rows/s", "n_gpus": world,
