@@ -86,6 +86,21 @@ QPB_API int qpb_sampler_dist_batch(qpb_sampler *s, const float *d_logits, int64_
                            int32_t *d_dist_ids, float *d_dist_p, int32_t *d_dist_count, int max_out,
                            int32_t *d_out_ids, void *stream);
 
+/* Replaces the speculative verification loop of Session::generate (src/chat.cpp:236-251) with its calls of
+ * qp::Sampler::accept (engine.h:36-39, src/sampler.cpp:65-73) and qp::Sampler::draw (src/sampler.cpp:58-63), for
+ * n_chains requests at once.  The distributions are rows written by qpb_sampler_dist_batch (with d_out_ids NULL, so
+ * that no random word is taken there): chain c owns the chain_rows consecutive rows from c * chain_rows; row i of a
+ * chain is the distribution after its i-th proposed token (history limited by that row's hist_len, engine.h:34).
+ * d_proposals [n_chains][chain_rows - 1]; d_n_proposals[c] of them are tested (NULL: all).  They are tested in order
+ * against the random stream of the chain's FIRST row; at the first rejection d_next[c] is the replacement token;
+ * if all pass, d_next[c] is drawn from the row after the last proposal.  d_accepted[c] = proposals accepted.
+ * Random words are consumed exactly as the reference does (none for p >= 1 or p == 0, none for a one-entry draw).
+ * Needs distributions in "most likely first" order: rows with top_k + window <= 500. */
+QPB_API int qpb_sampler_verify_chains(qpb_sampler *s, const int32_t *d_dist_ids, const float *d_dist_p,
+                                      const int32_t *d_dist_count, int max_out, int n_chains, int chain_rows,
+                                      const int32_t *d_proposals, const int32_t *d_n_proposals, int32_t *d_accepted,
+                                      int32_t *d_next, void *stream);
+
 /* The same call for callers that hold logits in host memory, as every qp::Model::step does
  * (include/qpack/qpack.h:137): copies h_logits / h_history to the GPU, samples, copies the ids back and
  * returns after they have arrived.  Synchronous; checks the device status. */

@@ -13,6 +13,7 @@
 #include "../../include/qpack_b200_sampler.h"
 #include "sample_stream_kernel.cuh"
 #include "sample_whole_kernel.cuh"
+#include "sample_verify.cuh"
 
 using namespace qpb;
 
@@ -619,6 +620,36 @@ int qpb_sampler_rng_set(qpb_sampler *s, int row, const uint64_t *h_state313) {
   const unsigned int drawn = (unsigned int)h_state313[MT_N];
   QPB_CUDA(s, cudaMemcpy(s->d_rng + (size_t)row * MT_N, h_state313, sizeof(uint64_t) * MT_N, cudaMemcpyHostToDevice));
   QPB_CUDA(s, cudaMemcpy(s->d_drawn + row, &drawn, sizeof(unsigned int), cudaMemcpyHostToDevice));
+  return QPB_OK;
+}
+
+int qpb_sampler_verify_chains(qpb_sampler *s, const int32_t *d_dist_ids, const float *d_dist_p, const int32_t *d_dist_count,
+                              int max_out, int n_chains, int chain_rows, const int32_t *d_proposals,
+                              const int32_t *d_n_proposals, int32_t *d_accepted, int32_t *d_next, void *stream) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!d_dist_ids || !d_dist_p || !d_dist_count || !d_accepted || !d_next || max_out <= 0 || n_chains <= 0 || chain_rows <= 0)
+    return fail(s, QPB_ERR_INVALID, "null pointer or size out of range");
+  if (chain_rows > 1 && !d_proposals) return fail(s, QPB_ERR_INVALID, "proposals pointer is null");
+  if ((long long)n_chains * chain_rows > s->max_rows) return fail(s, QPB_ERR_INVALID, "n_chains * chain_rows exceeds max_rows");
+  if (s->n_params == 0) return fail(s, QPB_ERR_INVALID, "qpb_sampler_set_params has not been called");
+  DeviceGuard g(s->device);
+  VerifyArgs a = {};
+  a.dist_ids = d_dist_ids;
+  a.dist_p = d_dist_p;
+  a.dist_count = d_dist_count;
+  a.max_out = max_out;
+  a.n_chains = n_chains;
+  a.chain_rows = chain_rows;
+  a.proposals = d_proposals;
+  a.n_proposals = d_n_proposals;
+  a.rng_state = s->d_rng;
+  a.rng_drawn = s->d_drawn;
+  a.accepted = d_accepted;
+  a.next = d_next;
+  a.status = s->d_status;
+  verify_chains_kernel<<<(n_chains + kVerifyWarps - 1) / kVerifyWarps, 32 * kVerifyWarps, 0, (cudaStream_t)stream>>>(a);
+  QPB_CUDA(s, cudaGetLastError());
+  s->launches++;
   return QPB_OK;
 }
 

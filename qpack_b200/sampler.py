@@ -133,6 +133,28 @@ class BatchSampler:
                                                   self._stream(stream)))
         return (ids, p, cnt, out) if draw else (ids, p, cnt)
 
+    def verify_chains(self, ids: torch.Tensor, p: torch.Tensor, cnt: torch.Tensor, chain_rows: int,
+                      proposals: torch.Tensor, n_proposals: Optional[torch.Tensor] = None, stream=None):
+        """The speculative verification loop of Session::generate (src/chat.cpp:236-251) over distributions from
+        dist(): rows [c * chain_rows, (c + 1) * chain_rows) form chain c, proposals [n_chains, chain_rows - 1] are
+        tested in order with qp::Sampler::accept against the random stream of the chain's first row.  Returns
+        (accepted [n_chains], next_token [n_chains])."""
+        assert ids.dtype == torch.int32 and p.dtype == torch.float32 and cnt.dtype == torch.int32
+        assert ids.is_contiguous() and p.is_contiguous() and ids.shape == p.shape
+        rows, max_out = ids.shape
+        assert rows % chain_rows == 0
+        n_chains = rows // chain_rows
+        if chain_rows > 1:
+            assert proposals.dtype == torch.int32 and proposals.is_contiguous() and tuple(proposals.shape) == (n_chains, chain_rows - 1)
+        if n_proposals is not None:
+            assert n_proposals.dtype == torch.int32 and n_proposals.numel() == n_chains
+        acc = torch.empty(n_chains, dtype=torch.int32, device=ids.device)
+        nxt = torch.empty(n_chains, dtype=torch.int32, device=ids.device)
+        self._ck(self._lib.qpb_sampler_verify_chains(self._h, ids.data_ptr(), p.data_ptr(), cnt.data_ptr(), max_out, n_chains,
+                                                     chain_rows, _ptr(proposals) if chain_rows > 1 else None,
+                                                     _ptr(n_proposals), acc.data_ptr(), nxt.data_ptr(), self._stream(stream)))
+        return acc, nxt
+
     def sample_host(self, logits: np.ndarray, history: Optional[np.ndarray] = None, hist_len=None,
                     out: Optional[np.ndarray] = None) -> np.ndarray:
         """The same for logits in host memory (numpy, or a pinned torch tensor's .numpy()): copies in, samples,

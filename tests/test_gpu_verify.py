@@ -1,0 +1,86 @@
+"""Speculative verification on the device (qpb_sampler_verify_chains) against the checker replaying the loop of
+Session::generate (src/chat.cpp:236-251): dist with a growing hist_len, accept per proposal with one random stream
+per request, the replacement or the final draw, and the number of random words taken."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import Oracle, Ref, make_params
+from qpack_b200.sampler import BatchSampler
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _chains(n_chains, k, V, rng):
+    base = 40
+    H = base + 1 + k
+    logits = (rng.standard_normal((n_chains * (k + 1), V)) * 2.0).astype(np.float32)
+    spikes = rng.integers(0, V, (n_chains * (k + 1), 6))
+    for r in range(logits.shape[0]):
+        logits[r, spikes[r]] += rng.uniform(5.0, 9.0, 6).astype(np.float32)
+    hist = rng.integers(0, V, (n_chains, H)).astype(np.int32)
+    params = make_params(n_chains, temperature=rng.choice([0.0, 0.7, 1.0], n_chains, p=[0.15, 0.5, 0.35]),
+                         top_k=rng.choice([1, 8, 40], n_chains), top_p=rng.choice([0.9, 1.0], n_chains),
+                         min_p=rng.choice([0.0, 0.05], n_chains), repeat_penalty=rng.choice([1.0, 1.1], n_chains),
+                         repeat_last_n=32, seed=np.arange(n_chains) + 900)
+    return base, logits, hist, params
+
+
+def _replay(cls, params_c, logits_c, hist_c, base, proposals_c, k_c):
+    """The reference loop for one request with one sampler object."""
+    o = cls(params_c)
+    acc, nxt = 0, -1
+    for i in range(k_c):
+        ids, pr = o.dist(logits_c[i], hist_c, base + 1 + i)
+        ok, repl = o.accept(ids, pr, int(proposals_c[i]))
+        if not ok:
+            nxt = repl
+            break
+        acc += 1
+    if nxt < 0:
+        ids, pr = o.dist(logits_c[acc], hist_c, base + 1 + acc)
+        nxt = o.draw(ids, pr)
+    drawn = o.words_drawn() if hasattr(o, "words_drawn") else None
+    return acc, nxt, drawn
+
+
+@pytest.mark.parametrize("V", [4099, 151936])
+def test_verify_chains_match_the_reference_loop(V):
+    rng = np.random.default_rng(21)
+    n_chains, k = 40, 5
+    base, logits, hist, params = _chains(n_chains, k, V, rng)
+    rows = n_chains * (k + 1)
+    # proposals: mostly tokens the row's distribution holds (so that both outcomes occur), some that it does not
+    proposals = np.empty((n_chains, k), np.int32)
+    n_prop = rng.integers(0, k + 1, n_chains).astype(np.int32)
+    n_prop[:8] = k
+    for c in range(n_chains):
+        o = Oracle(params[c:c + 1])
+        for i in range(k):
+            ids, pr = o.dist(logits[c * (k + 1) + i], hist[c], base + 1 + i)
+            u = rng.random()
+            proposals[c, i] = ids[0] if u < 0.6 else (ids[min(len(ids) - 1, 1 + int(rng.integers(0, 3)))] if u < 0.85
+                                                      else int(rng.integers(0, V)))
+    exp = [_replay(Oracle, params[c:c + 1], logits[c * (k + 1):(c + 1) * (k + 1)], hist[c], base, proposals[c], int(n_prop[c]))
+           for c in range(n_chains)]
+    if Ref.available():  # the compiled reference agrees with the checker on the whole loop
+        for c in range(0, n_chains, 5):
+            r = _replay(Ref, params[c:c + 1], logits[c * (k + 1):(c + 1) * (k + 1)], hist[c], base, proposals[c], int(n_prop[c]))
+            assert r[:2] == exp[c][:2], c
+
+    row_params = np.repeat(params, k + 1)
+    bs = BatchSampler(rows, 0)
+    bs.set_params(row_params)
+    d_x = torch.from_numpy(logits).to(DEV)
+    d_h = torch.from_numpy(np.repeat(hist, k + 1, axis=0)).to(DEV)
+    hl = (base + 1 + np.tile(np.arange(k + 1), n_chains)).astype(np.int32)
+    ids, p, cnt = bs.dist(d_x, d_h, torch.from_numpy(hl).to(DEV), max_out=64, draw=False)
+    acc, nxt = bs.verify_chains(ids, p, cnt, k + 1, torch.from_numpy(proposals).to(DEV), torch.from_numpy(n_prop).to(DEV))
+    bs.check()
+    acc, nxt = acc.cpu().numpy(), nxt.cpu().numpy()
+    for c in range(n_chains):
+        assert (int(acc[c]), int(nxt[c])) == exp[c][:2], (c, acc[c], nxt[c], exp[c])
+        assert int(bs.rng_get(c * (k + 1))[312]) == exp[c][2], ("random words taken", c)
+    assert len({e[0] for e in exp}) > 2  # rejections at different depths and fully accepted chains both occur
+    bs.close()
