@@ -76,6 +76,15 @@ QPB_API int qpb_sampler_sample_batch(qpb_sampler *s, const float *d_logits, int6
                              const int32_t *d_history, int64_t hist_stride, const int32_t *d_hist_len,
                              int hist_len_all, int32_t *d_out_ids, void *stream);
 
+/* qp::Sampler::sample followed by the caller's hist_.push_back(token) (src/chat.cpp:228), on the device: row r is
+ * sampled with its d_hist_len[r] visible history ids, then the token is written to d_history[r][d_hist_len[r]] and
+ * d_hist_len[r] is incremented, so that a decode loop can run step after step (e.g. in one CUDA graph) without a
+ * host round trip; the token is also stored in d_out_ids[r] when that is not NULL.  A row whose history buffer is
+ * full keeps its history and raises an error at the next qpb_sampler_check. */
+QPB_API int qpb_sampler_sample_append(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
+                                      int32_t *d_history, int64_t hist_stride, int32_t *d_hist_len,
+                                      int32_t *d_out_ids, void *stream);
+
 /* Replaces qp::Sampler::dist (engine.h:31-34, src/sampler.cpp:29-56): row r's distribution as (id, probability)
  * pairs, most likely first, into d_dist_ids / d_dist_p [n_rows][max_out] (first max_out pairs) with the full
  * pair count in d_dist_count[r].  If d_out_ids is not NULL the draw of qp::Sampler::draw (src/sampler.cpp:58-63)

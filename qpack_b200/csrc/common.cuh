@@ -23,6 +23,7 @@ enum : int {
   ST_COPY_TIMEOUT = 1,    // a bounded wait on a bulk copy gave up
   ST_CAPACITY = 2,        // a candidate buffer would have overflowed (host sizing bug)
   ST_PEN_TABLE_FULL = 4,  // penalty hash table full (host sizing bug)
+  ST_HISTORY_FULL = 8,    // a sampled token could not be appended: the row's history buffer is full
 };
 
 constexpr int MT_N = 312;

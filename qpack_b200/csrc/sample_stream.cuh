@@ -54,6 +54,8 @@ struct StreamArgs {
   unsigned int *rng_drawn;        // [rows]
   int *out_ids;            // [rows] (may be nullptr when draw == 0)
   int draw;                // 1: make the draw (takes a random word unless one entry survives); 0: distribution only
+  int append;              // 1: the drawn token is appended to the row's history and hist_len[row] incremented (both
+                           //    then are the caller's mutable buffers): a decode loop without a host round trip
   int *dist_ids;           // optional [rows][max_out]
   float *dist_p;           // optional [rows][max_out]
   int *dist_count;         // optional [rows]
@@ -77,6 +79,21 @@ struct StreamArgs {
   int *status;
   long long *phase_clk;    // optional [rows][16]: SM clock stamps of the leader CTA's phases (latency breakdown)
 };
+
+// The sampled token of a row leaves the kernel here (one thread per row).
+__device__ __forceinline__ void emit_token(const StreamArgs &a, int row, int id) {
+  if (a.out_ids) a.out_ids[row] = id;
+  if (a.append) {
+    int *len = const_cast<int *>(a.hist_len) + row;
+    const int hn = *len;
+    if (hn >= 0 && hn < a.hist_stride) {
+      const_cast<int *>(a.history)[(size_t)row * a.hist_stride + hn] = id;
+      *len = hn + 1;
+    } else {
+      atomicOr(a.status, ST_HISTORY_FULL);
+    }
+  }
+}
 
 // ---- penalty set: open-addressing hash set of the distinct in-range ids of the window (sampler.cpp:32-38) ------
 __device__ __forceinline__ uint32_t pen_hash(int id, int slots) { return ((uint32_t)id * 2654435761u) & (uint32_t)(slots - 1); }
@@ -508,7 +525,7 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
   if (greedy) {  // sampler.cpp:45; draw() of a one-entry distribution takes no random word (sampler.cpp:59)
     if (threadIdx.x == 0) {
       const int id = comp_id(sorted[0]);
-      if (a.out_ids) a.out_ids[row] = id;
+      if (a.draw) emit_token(a, row, id);
       if (a.dist_count) a.dist_count[row] = 1;
       if (a.dist_ids && a.max_out > 0) { a.dist_ids[(size_t)row * a.max_out] = id; a.dist_p[(size_t)row * a.max_out] = 1.f; }
     }
@@ -651,7 +668,7 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
     }
   }
   if (lane == 0) {
-    if (a.draw && a.out_ids) a.out_ids[row] = comp_id(sorted[pick]);
+    if (a.draw) emit_token(a, row, comp_id(sorted[pick]));
     if (a.dist_count) a.dist_count[row] = keep;
   }
   if (a.dist_ids) {

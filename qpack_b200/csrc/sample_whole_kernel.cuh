@@ -199,7 +199,7 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
 
   // ---- outputs ----
   if (leader0) {
-    if (a.draw && a.out_ids) a.out_ids[row] = picked;
+    if (a.draw) emit_token(a, row, picked);
     if (a.dist_count) a.dist_count[row] = (int)keep;
   }
   if (a.dist_ids && a.max_out > 0) {  // the kept pairs, in no particular order

@@ -264,6 +264,7 @@ struct Inputs {
   int64_t hist_stride;
   const int32_t *d_hist_len;
   int hist_len_all;
+  bool append = false;  // append the drawn token to the row's history (d_history / d_hist_len are then written)
 };
 
 int check_inputs(qpb_sampler *s, const Inputs &in, bool need_logits) {
@@ -291,6 +292,7 @@ void fill_common(qpb_sampler *s, const Inputs &in, StreamArgs &a) {
   a.hist_stride = in.hist_stride;
   a.hist_len = in.d_hist_len;
   a.hist_len_all = in.d_history ? in.hist_len_all : 0;
+  a.append = in.append ? 1 : 0;
   a.rng_state = s->d_rng;
   a.rng_drawn = s->d_drawn;
   a.status = s->d_status;
@@ -482,6 +484,16 @@ int qpb_sampler_dist_batch(qpb_sampler *s, const float *d_logits, int64_t row_st
                   d_out_ids != nullptr, (cudaStream_t)stream);
 }
 
+int qpb_sampler_sample_append(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
+                              int32_t *d_history, int64_t hist_stride, int32_t *d_hist_len, int32_t *d_out_ids,
+                              void *stream) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!d_history || !d_hist_len) return fail(s, QPB_ERR_INVALID, "history and hist_len buffers are required");
+  Inputs in{d_logits, row_stride, n_rows, vocab, vocab, 0, d_history, hist_stride, d_hist_len, 0};
+  in.append = true;
+  return run_rows(s, in, nullptr, nullptr, nullptr, 0, d_out_ids, true, (cudaStream_t)stream);
+}
+
 int qpb_sampler_check(qpb_sampler *s, void *stream) {
   if (!s) return QPB_ERR_INVALID;
   DeviceGuard g(s->device);
@@ -491,6 +503,7 @@ int qpb_sampler_check(qpb_sampler *s, void *stream) {
   if (st == 0) return QPB_OK;
   QPB_CUDA(s, cudaMemsetAsync(s->d_status, 0, sizeof(int), (cudaStream_t)stream));
   if (st & ST_COPY_TIMEOUT) return fail(s, QPB_ERR_DEVICE_TIMEOUT, "a device-side wait on a bulk copy gave up");
+  if (st == ST_HISTORY_FULL) return fail(s, QPB_ERR_INVALID, "a sampled token could not be appended: history buffer full");
   char buf[96];
   snprintf(buf, sizeof buf, "device-side capacity check failed (status 0x%x)", st);
   return fail(s, QPB_ERR_INTERNAL, buf);

@@ -133,6 +133,18 @@ class BatchSampler:
                                                   self._stream(stream)))
         return (ids, p, cnt, out) if draw else (ids, p, cnt)
 
+    def sample_append(self, logits: torch.Tensor, history: torch.Tensor, hist_len: torch.Tensor,
+                      out: Optional[torch.Tensor] = None, stream=None) -> Optional[torch.Tensor]:
+        """Samples every row and appends the token to the row's history on the device (history [B, cap] int32 and
+        hist_len [B] int32 are updated in place): one step of a decode loop without a host round trip."""
+        assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+        assert history.dtype == torch.int32 and history.dim() == 2 and history.is_contiguous()
+        assert hist_len.dtype == torch.int32 and hist_len.numel() == logits.shape[0]
+        B, V = logits.shape
+        self._ck(self._lib.qpb_sampler_sample_append(self._h, logits.data_ptr(), logits.stride(0), B, V, history.data_ptr(),
+                                                     history.shape[1], hist_len.data_ptr(), _ptr(out), self._stream(stream)))
+        return out
+
     def verify_chains(self, ids: torch.Tensor, p: torch.Tensor, cnt: torch.Tensor, chain_rows: int,
                       proposals: torch.Tensor, n_proposals: Optional[torch.Tensor] = None, stream=None):
         """The speculative verification loop of Session::generate (src/chat.cpp:236-251) over distributions from

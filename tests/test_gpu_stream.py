@@ -105,6 +105,40 @@ def test_single_row_loop(golden):
     bs.close()
 
 
+def test_single_row_loop_resident_on_the_device(golden):
+    """The same loop with the history kept and extended on the device (qpb_sampler_sample_append), all steps
+    captured in one CUDA graph: no host round trip between steps, same tokens as the reference's loop."""
+    params, hist0 = synth.single_row_loop()
+    steps = min(200, len(golden["loop_ids"]))
+    bs = BatchSampler(1, 0)
+    bs.set_params(params)
+    logits = torch.from_numpy(np.concatenate([synth.single_row_step(i) for i in range(steps)], 0)).to(DEV)
+    hist = torch.zeros((1, 64 + steps), dtype=torch.int32, device=DEV)
+    hist[0, :64] = torch.from_numpy(hist0).to(DEV)
+    hlen = torch.full((1,), 64, dtype=torch.int32, device=DEV)
+    bs.sample_append(logits[0:1], hist, hlen)  # warm-up call outside the capture (first-use set-up), then rewind
+    torch.cuda.synchronize()
+    bs.set_params(params)
+    hlen.fill_(64)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for i in range(steps):
+                bs.sample_append(logits[i:i + 1], hist, hlen)
+        g.replay()
+    side.synchronize()
+    bs.check()
+    assert int(hlen.item()) == 64 + steps
+    assert hist[0, 64:].cpu().numpy().tolist() == golden["loop_ids"][:steps].tolist()
+    # a full buffer is reported, not overrun
+    bs.sample_append(logits[0:1], hist, hlen)
+    with pytest.raises(SamplerError):
+        bs.check()
+    bs.close()
+
+
 def test_rng_state_get_set_resumes_stream():
     wl = synth.serving_batch(rows=4)
     d_x = torch.from_numpy(wl.logits).to(DEV)
