@@ -170,7 +170,8 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       if (early_pen) npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
       // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
       const long long sample = (long long)kSampleTiles * kTile;
-      const long long aim = lean ? min((long long)Mloc, (long long)K + 16 + K / 4) : (long long)Mloc;
+      // (a cluster judges the merged list as a whole, so each of its CTAs only aims at its share)
+      const long long aim = lean ? min((long long)Mloc, ((long long)K + 16 + K / 4 + csize - 1) / csize) : (long long)Mloc;
       long long r = (9LL * aim * sample + 4LL * (s1 - s0) - 1) / (4LL * (s1 - s0));
       r = r < (lean ? kLeanMinRank : 16) ? (lean ? kLeanMinRank : 16) : r;
       booted = Mloc < Vt && r <= kThreads * 3 / 4;  // two maxima per thread hold the sample's best few dozen well enough

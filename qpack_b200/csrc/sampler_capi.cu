@@ -154,9 +154,9 @@ int merge_cap(int nt) { return nt == 128 ? Stream<128>::kMergeCap : Stream<256>:
 
 int pick_cluster(const qpb_sampler *s, int rows) {
   // A single CTA takes a few tens of microseconds over a row, so while SMs are to spare a row is split over a
-  // cluster: as wide as keeps the launch at or below three CTAs per SM.
+  // cluster (measured best: 8 CTAs up to ~2.6 CTAs per SM in the launch, 4 up to 3, 2 up to 4).
   int c = s->cluster;
-  if (!c) c = 4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 3LL * s->sm_count ? 2 : 1);
+  if (!c) c = 80LL * rows <= 26LL * s->sm_count ? 8 : (4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 4LL * s->sm_count ? 2 : 1));
   const int nt = plan_stream(s, (long long)rows * c, 64).nt;
   return c < max_cluster(nt) ? c : max_cluster(nt);
 }
