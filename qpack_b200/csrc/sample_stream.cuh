@@ -66,6 +66,7 @@ struct StreamArgs {
   int cand_rows;           // row dimension of cand_io
   int pen_slots;           // penalty hash slots (power of two)
   int log2_stages;         // ring depth = 1 << log2_stages (1 .. 3)
+  int inbox_off;           // cluster launches: byte offset of the leader's inbox in dynamic shared memory
   // Row pieces (one CTA per cluster only).  units_per_cta > 0: the rows of this launch, cut into tiles of kTile
   // columns and laid end to end, are dealt out in equal runs of units_per_cta tiles to the CTAs of the grid; a row
   // that straddles CTAs is sampled in pieces, each piece leaves its best candidates in piece_cand, and the CTA

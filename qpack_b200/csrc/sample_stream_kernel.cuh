@@ -28,6 +28,9 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
   cg::cluster_group cluster = cg::this_cluster();
   const int csize = (int)cluster.num_blocks();
   const int crank = (int)cluster.block_rank();
+  // cluster launches only: one slot per other CTA of the cluster for its winners, then (count, guess key) per slot
+  unsigned long long *inbox = reinterpret_cast<unsigned long long *>(smem_raw + a.inbox_off);
+  int *inbox_meta = reinterpret_cast<int *>(inbox + (size_t)(csize - 1) * kSmallMaxM);
   const int tid = threadIdx.x, lane = tid & 31;
   const int Vt = a.vocab_total;
   const uint32_t ring_s = smem_u32(ring), full_s = smem_u32(&S.full[0]);
@@ -44,7 +47,8 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
   bool failed = false;  // a bounded wait on a copy gave up
 
   // ---- one piece: columns [s0, s1) of `row` (local columns of this GPU) ----------------------------------------
-  auto do_piece = [&](const int row, const int s0, const int s1, const int npieces, const int pi, long long *clk_arg) {
+  auto do_piece = [&](const int row, int s0, int s1, const int npieces, const int pi, long long *clk_arg) {
+    int cs = csize;  // CTAs that share the row (1 once a cluster's leader has taken the row over)
     long long *const clk = TIMED ? clk_arg : nullptr;  // phase stamps only exist in the timed instantiation
 #define QPB_STAMP(k) do { if (clk) clk[k] = clock64(); } while (0)
     QPB_STAMP(0);
@@ -54,8 +58,8 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     const RowParams p = a.params[a.params_per_row ? row : 0];
     long long hn = (a.history == nullptr) ? 0 : (a.hist_len ? a.hist_len[row] : a.hist_len_all);
     const float *rowp = a.logits + (size_t)row * a.row_stride;
-    const int n_tiles = (MODE == MODE_MERGE) ? 0 : (s1 - s0 + kTile - 1) / kTile;
-    const bool base_aligned = ((reinterpret_cast<uintptr_t>(rowp + s0) & 15u) == 0);
+    int n_tiles = (MODE == MODE_MERGE) ? 0 : (s1 - s0 + kTile - 1) / kTile;
+    bool base_aligned = ((reinterpret_cast<uintptr_t>(rowp + s0) & 15u) == 0);
 
     auto tile_len = [&](int t) { return min(kTile, s1 - s0 - t * kTile); };
     auto tile_bulk = [&](int t) { return base_aligned && ((tile_len(t) & 3) == 0); };
@@ -73,9 +77,17 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     // fewer columns pass than are needed, the piece is streamed again without it.  The sample is kSampleChunks
     // short runs per stage, evenly spaced over the piece (logits correlate with the token id: frequent tokens sit
     // at low ids), one bulk copy each, issued by as many threads.
-    const bool can_boot = MODE != MODE_MERGE && base_aligned && n_tiles > 2 * kSampleTiles;
+    const bool can_boot = MODE != MODE_MERGE && base_aligned &&
+                          n_tiles > ((csize > 1 && nst >= 2 * kSampleTiles) ? kSampleTiles : 2 * kSampleTiles);
     int g0 = g_next;  // ring slot of the piece's tile 0 (moved past the sample below)
-    if (can_boot) {
+    // The short slice of a cluster CTA is not sampled separately when the ring is deep enough: its first tiles are
+    // fetched once, serve as the sample and are then scanned where they lie, with the following tiles already on
+    // their way.  (The cluster's leader judges the merged list, so a slice's own guess need not be representative.)
+    const bool first_tiles_sample = can_boot && csize > 1 && nst >= 2 * kSampleTiles;
+    if (first_tiles_sample) {
+      if (tid == 0)
+        for (int j = 0; j < nst; ++j) issue(j, g0 + j);
+    } else if (can_boot) {
       constexpr int kRuns = kSampleTiles * kSampleChunks, kRunLen = kTile / kSampleChunks;  // floats per run
       if (tid < kRuns) {
         const int j = tid / kSampleChunks, g = g0 + j;
@@ -98,7 +110,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     }
     // RNG words and the first history id of the window: fetched now, used only if this CTA finishes the row
     // (the RNG words are only pulled towards L2 here: holding them in registers through the scan costs occupancy)
-    if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == 0 && a.draw) {
+    if (MODE != MODE_LOCAL_TOPM && crank == 0 && tid == kThreads - 1 && a.draw) {  // (not the thread that issues copies)
       const unsigned int d = a.rng_drawn[row];
       const unsigned long long *mt = a.rng_state + (size_t)row * MT_N;
       const int k = (int)(d % MT_N);
@@ -127,7 +139,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     const long long wlen = use_pen ? hn - hfrom : 0;
     int Mloc = (int)min((long long)Vt, (long long)K + wlen);
     if (Mloc >= Vt / 4) Mloc = Vt;
-    const int need = min(Mloc, s1 - s0);  // columns this piece must deliver
+    int need = min(Mloc, s1 - s0);  // columns this piece must deliver
     // A CTA that finishes its row alone, with a penalty that only lowers values (or none), can aim lower: the K
     // best after the penalty all have a RAW value above any threshold that at least K penalised values exceed
     // (penalised <= raw), so it is enough to collect the columns above a threshold aimed at K + a margin and to
@@ -164,9 +176,11 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;  // set-up of block_guess_threshold
       if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
       __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
-      g0 += kSampleTiles;  // start the stream proper while the threshold is worked out (its tiles are fetched again)
-      if (tid == 0)
-        for (int j = 0; j < nst; ++j) issue(j, g0 + j);
+      if (!first_tiles_sample) {
+        g0 += kSampleTiles;  // start the stream proper while the threshold is worked out (its tiles are fetched again)
+        if (tid == 0)
+          for (int j = 0; j < nst; ++j) issue(j, g0 + j);
+      }
       if (early_pen) npen = pen_build(pen_tab, a.pen_slots, &S.pen_unique, hrow, hfrom, hn, first_id, Vt, a.status, S.pen_bloom);
       // rank of the threshold within the sample: 2.25 x the share of the needed columns expected in the sample
       const long long sample = (long long)kSampleTiles * kTile;
@@ -386,7 +400,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       bool ok = true, guess = false;
       if (booted) {
         if (lean && !shrunk) {
-          if (csize == 1) {
+          if (cs == 1) {
             const int nl = min(S.cand_count, kCandCap);
             build_pen_now();
             if (have_vb) {
@@ -407,49 +421,60 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
           ok = S.cand_count >= need;
         }
       }
-      if (ok && csize > 1 && MODE == MODE_SAMPLE) {
-        // ---- cluster merge: every CTA pushes its list into the leader's over DSMEM ----
+      if (ok && cs > 1 && MODE == MODE_SAMPLE) {
+        // ---- cluster merge: every other CTA leaves its winners in its inbox slot of the leader's shared memory
+        // (DSMEM stores), one cluster barrier makes them visible, and it is done; the leader judges alone ----
         n = min(S.cand_count, kCandCap);
         if (n > Mloc) { n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count); guess = false; }
-        StreamSmem *L = cluster.map_shared_rank(&S, 0);
-        if (crank == 0 && tid == 0) { S.sel[3] = guess ? f2key(thr) : 0u; S.misc[1] = 0; }
-        cluster.sync();  // the leader's ring is idle, its own list and its verdict words are set
+        const uint32_t gkey = guess ? f2key(thr) : 0u;
         if (crank != 0) {
-          if (tid == 0) {
-            S.misc[0] = atomicAdd(&L->cand_count, n);
-            if (guess) atomicMax(&L->sel[3], f2key(thr));
-          }
-          __syncthreads();
-          const int base = S.misc[0];
-          for (int i = tid; i < n; i += kThreads)
-            if (base + i < kMergeCap) L->cand[base + i] = S.cand[i];
-          if (base + n > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
+          unsigned long long *slot = cluster.map_shared_rank(inbox + (size_t)(crank - 1) * kSmallMaxM, 0);
+          int *meta = cluster.map_shared_rank(inbox_meta + 2 * (crank - 1), 0);
+          for (int i = tid; i < n; i += kThreads) slot[i] = S.cand[i];
+          if (tid == 0) { meta[0] = n; meta[1] = (int)gkey; }
+          cluster.sync();
+          return;
         }
         cluster.sync();  // every list has arrived
-        const uint32_t tmax = L->sel[3];  // highest guessed threshold in the cluster (0: nobody guessed)
+        uint32_t tmax = gkey;  // highest guessed threshold in the cluster (0: nobody guessed)
+        for (int r = 1; r < cs; ++r) {
+          const int cr = inbox_meta[2 * (r - 1)];
+          tmax = max(tmax, (uint32_t)inbox_meta[2 * (r - 1) + 1]);
+          const unsigned long long *src = inbox + (size_t)(r - 1) * kSmallMaxM;
+          for (int i = tid; i < cr; i += kThreads)
+            if (n + i < kMergeCap) S.cand[n + i] = src[i];
+          n += cr;
+        }
+        if (n > kMergeCap) { if (tid == 0) atomicOr(a.status, ST_CAPACITY); n = kMergeCap; }
+        __syncthreads();
         bool redo = false;
         if (tmax != 0u) {
-          if (crank == 0) {
-            // lists of guessing CTAs hold every column above their threshold, the others their exact best Mloc:
-            // the merged list is good if K entries still exceed the highest guess once penalised
-            n = min(S.cand_count, kMergeCap);
-            build_pen_now();
-            if (npen > 0) penalise_candidates(S.cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
-            penalised = true;
-            if (count_above(n, tmax) < min(K, Vt) && tid == 0) S.misc[1] = 1;
+          // lists of guessing CTAs hold every column above their threshold, the others their exact best Mloc:
+          // the merged list is good if K entries still exceed the highest guess once penalised
+          build_pen_now();
+          if (have_vb && n <= Mloc) {
+            // (counted into the leader's value buckets on the way: the finish can start from the histogram)
+            penalise_and_count(S.cand, n, pen_tab, a.pen_slots, S.pen_bloom, npen > 0, p.repeat_penalty, S.vbp, S.hist);
+            hist_ok = true;
+          } else if (npen > 0) {
+            penalise_candidates(S.cand, n, pen_tab, a.pen_slots, S.pen_bloom, p.repeat_penalty);
           }
-          cluster.sync();  // the verdict is in
-          redo = L->misc[1] != 0;
+          penalised = true;
+          redo = count_above(n, tmax) < min(K, Vt);
         }
         if (!redo) {
-          if (crank != 0) return;
-          n = min(S.cand_count, kMergeCap);
           n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
           break;
         }
-        ok = false;  // every CTA of the cluster streams its slice again, exactly
+        // The guesses were too high.  The other CTAs have left: the leader takes the whole row over on its own.
+        ok = false;
         penalised = false;
-        cluster.sync();  // nobody resets anything before everybody has read the verdict
+        cs = 1;
+        s0 = 0;
+        s1 = a.vocab;
+        n_tiles = (s1 - s0 + kTile - 1) / kTile;
+        base_aligned = ((reinterpret_cast<uintptr_t>(rowp) & 15u) == 0);
+        need = min(Mloc, s1 - s0);
       }
       if (ok) break;
       __syncthreads();
@@ -498,10 +523,10 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       if (S.cand_count > kMergeCap && tid == 0) atomicOr(a.status, ST_CAPACITY);
     }
 
-    const bool merged = csize > 1 && MODE == MODE_SAMPLE;  // the leader already holds the merged, cut list
+    const bool merged = cs > 1 && MODE == MODE_SAMPLE;  // the leader already holds the merged, cut list
     if (!merged) n = min(S.cand_count, MODE == MODE_MERGE ? kMergeCap : kCandCap);
     // Lists that travel (piece scratch, all-gather) are cut to the streaming budget first.
-    const bool travels = !merged && (csize > 1 || npieces > 1 || MODE != MODE_SAMPLE);
+    const bool travels = !merged && (cs > 1 || npieces > 1 || MODE != MODE_SAMPLE);
     if (travels) n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count);
     QPB_STAMP(3);
 
@@ -605,6 +630,15 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       per = (per + 3) & ~3;
       s0 = min(a.vocab, crank * per);
       s1 = min(a.vocab, s0 + per);
+      if (csize > 1 && per >= 4 * kTile) {
+        // The leader also builds the penalty set and fetches the random words, which makes it the last to reach
+        // the cluster's barrier: its slice is two tiles shorter (but three tiles at least), the others share the rest.
+        const int lead = max(3 * kTile, per - 2 * kTile);
+        int rest = (a.vocab - lead + csize - 2) / (csize - 1);
+        rest = (rest + 3) & ~3;
+        s0 = crank == 0 ? 0 : min(a.vocab, lead + (crank - 1) * rest);
+        s1 = crank == 0 ? lead : min(a.vocab, s0 + rest);
+      }
       clk = (a.phase_clk && crank == 0 && tid == 0) ? a.phase_clk + (size_t)row * 16 : nullptr;
       if (TIMED && clk) { clk[11] = 0; clk[12] = 0; clk[13] = 0; clk[14] = 0; clk[15] = 0; }
       u = u1;

@@ -136,17 +136,27 @@ int route_rows(qpb_sampler *s, int n_rows, int vocab_total, long long hist_cap, 
 struct StreamPlan {
   int nt, lg;
 };
-size_t stream_smem(const StreamPlan &pl, int pen_slots) {
+// dynamic shared memory of a CTA: the fixed structure, ring stages beyond the first two, the penalty table and, in
+// cluster launches, the inbox (a slot per other CTA of the cluster, then a (count, key) pair per slot)
+size_t stream_inbox_off(const StreamPlan &pl, int pen_slots) {
   const size_t base = pl.nt == 128 ? sizeof(Stream<128>::StreamSmem) : sizeof(Stream<256>::StreamSmem);
-  return base + (size_t)((1 << pl.lg) - kMinStages) * (size_t)pl.nt * 16 * 4 + (size_t)pen_slots * sizeof(int);
+  const size_t end = base + (size_t)((1 << pl.lg) - kMinStages) * (size_t)pl.nt * 16 * 4 + (size_t)pen_slots * sizeof(int);
+  return (end + 15) & ~(size_t)15;
+}
+size_t stream_smem(const StreamPlan &pl, int pen_slots, int cluster = 1) {
+  const size_t off = stream_inbox_off(pl, pen_slots);
+  if (cluster <= 1) return off;
+  return off + (size_t)(cluster - 1) * (kSmallMaxM * sizeof(unsigned long long) + 2 * sizeof(int));
 }
 constexpr size_t kSmemLimit = 227 * 1024;
-StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots) {
+StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots, int cluster = 1) {
   StreamPlan pl;
   pl.nt = s->force_threads ? s->force_threads : (ctas > 4LL * s->sm_count ? 128 : 256);
   if (s->force_log2_stages) pl.lg = s->force_log2_stages;
-  else pl.lg = 1;  // deeper rings measured no faster: one CTA is bound by its own scan, many CTAs by HBM
-  while (pl.lg > 1 && stream_smem(pl, pen_slots) > kSmemLimit) pl.lg--;
+  else pl.lg = (pl.nt == 256 && cluster > 1 && ctas <= 2LL * s->sm_count) ? 2 : 1;
+  // (four stages let a cluster CTA fetch the head of its short slice once and use it as its threshold sample;
+  // otherwise deeper rings measured no faster: one CTA is bound by its own scan, many CTAs by HBM)
+  while (pl.lg > 1 && stream_smem(pl, pen_slots, cluster) > kSmemLimit) pl.lg--;
   return pl;
 }
 int max_cluster(int nt) { return nt == 128 ? Stream<128>::kMaxCluster : Stream<256>::kMaxCluster; }
@@ -154,9 +164,10 @@ int merge_cap(int nt) { return nt == 128 ? Stream<128>::kMergeCap : Stream<256>:
 
 int pick_cluster(const qpb_sampler *s, int rows) {
   // A single CTA takes a few tens of microseconds over a row, so while SMs are to spare a row is split over a
-  // cluster (measured best: 8 CTAs up to ~2.6 CTAs per SM in the launch, 4 up to 3, 2 up to 4).
+  // cluster, as wide as the shared memory of its CTAs (the leader's inbox grows with the cluster) lets the launch
+  // stay resident at once: 8 CTAs up to two CTAs per SM, 4 up to three, 2 up to four (measured best).
   int c = s->cluster;
-  if (!c) c = 80LL * rows <= 26LL * s->sm_count ? 8 : (4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 4LL * s->sm_count ? 2 : 1));
+  if (!c) c = 8LL * rows <= 2LL * s->sm_count ? 8 : (4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 4LL * s->sm_count ? 2 : 1));
   const int nt = plan_stream(s, (long long)rows * c, 64).nt;
   return c < max_cluster(nt) ? c : max_cluster(nt);
 }
@@ -240,14 +251,15 @@ int launch_stream_nt(qpb_sampler *s, const StreamArgs &args, int rows, int clust
 template <int MODE>
 int launch_stream(qpb_sampler *s, const StreamArgs &args_in, int rows, int cluster, cudaStream_t st, int nt) {
   StreamArgs args = args_in;
-  StreamPlan pl = plan_stream(s, (long long)rows * cluster, args.pen_slots);
+  StreamPlan pl = plan_stream(s, (long long)rows * cluster, args.pen_slots, cluster);
   if (nt) {  // the caller counted tiles for this block size
     pl.nt = nt;
     if (nt == 128) pl.lg = 1;
   }
   if (cluster > max_cluster(pl.nt)) return fail(s, QPB_ERR_INVALID, "cluster too large for the block size");
   args.log2_stages = pl.lg;
-  const size_t smem = stream_smem(pl, args.pen_slots);
+  args.inbox_off = (int)stream_inbox_off(pl, args.pen_slots);
+  const size_t smem = stream_smem(pl, args.pen_slots, cluster);
   if (smem > kSmemLimit) return fail(s, QPB_ERR_UNSUPPORTED, "history window too large for the penalty table");
   if (pl.nt == 128) return launch_stream_nt<128, MODE>(s, args, rows, cluster, smem, st);
   return launch_stream_nt<256, MODE>(s, args, rows, cluster, smem, st);
