@@ -75,8 +75,8 @@ def adversarial_rows(V, rng):
     quant = np.round(base * 4.0) / 4.0  # heavy ties across the whole range
     rows["quantised"] = quant.astype(np.float32)
     spike = base.copy()
-    spike[V // 4 + 8:V // 4 + 28] = 50.0  # a few huge values at the head of one cluster slice: its own guess is far too high
-    rows["slice_head_spike"] = spike
+    spike[100:180:4] = 50.0  # a few huge values at the head of the row: a guess taken from there is far too high, and
+    rows["front_spike"] = spike  # a cluster's leader (whose slice starts at 0) has to take the row over
     plateau = base.copy()
     plateau[rng.integers(0, V, 5000)] = 6.0  # thousands of equal maxima: the K best are decided by index
     rows["plateau"] = plateau

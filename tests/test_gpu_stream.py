@@ -199,7 +199,7 @@ def test_adversarial_rows(config):
         params = synth.make_params(B, temperature=0.8, top_k=top_k, top_p=0.95, min_p=0.01, repeat_penalty=rp,
                                    repeat_last_n=96, seed=np.arange(B) + 11)
         exp = Oracle.sample_rows(params, logits, hist, None, max_out=256)
-        for cluster in (1, 4):
+        for cluster in (1, 4, 8):
             got = run_device(params, logits, hist, None, max_out=256, cluster=cluster, config=config)
             rep = compare_rows(*got, exp)
             assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (top_k, rp, cluster, rep)
