@@ -210,6 +210,7 @@ struct __align__(128) StreamSmem {
   int pen_unique;
   int misc[2];
   float vbp[2];  // value buckets (lo, scale) of the candidates collected with a guessed threshold
+  float second[3];  // a second, lower guess (NaN: none) and its value buckets
   alignas(128) unsigned long long cand[kCandCap];  // candidates; the ring follows directly so that a merge can use both
   alignas(128) float ring[kMinStages][kTile];      // further stages follow the structure
 };
@@ -331,8 +332,10 @@ static __device__ __forceinline__ int block_keep_top(unsigned long long *c, int 
 // it); NaN means "no guess" (a flat or non-finite sample).  r <= kThreads.  hist must be zero on entry (it is
 // left zero), sel[0] = 0xffffffff, sel[1] = 0, sel[3] = NaN bits, and a barrier must lie between that set-up and this call.
 // vb_out[0..1] receive the buckets (lo, scale) that the candidates above the guess are later sorted with: from the
-// guess up to as far above the sample's maximum as that lies above the guess.
-static __device__ float block_guess_threshold(float m1, float m2, int r, uint32_t *hist, uint32_t *sel, float *vb_out) {
+// guess up to as far above the sample's maximum as that lies above the guess.  With r2 > 0 a second, lower guess
+// at that rank is left in second[0] with its buckets in second[1..2], for the case that the first one fails.
+static __device__ float block_guess_threshold(float m1, float m2, int r, int r2, uint32_t *hist, uint32_t *sel,
+                                              float *vb_out, float *second) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t k1 = f2key(m1);
   block_key_range(k1, k1, sel);
@@ -350,21 +353,30 @@ static __device__ float block_guess_threshold(float m1, float m2, int r, uint32_
     warp_bins_above(hist, lane, loc, own, above);
 #pragma unroll
     for (int k = 0; k < 8; ++k) hist[8 * lane + k] = 0;
-    if (above < (uint32_t)r && (uint32_t)r <= above + own) {
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const uint32_t rank = (uint32_t)(which ? r2 : r);
+      if (rank == 0 || !(above < rank && rank <= above + own)) continue;
       uint32_t acc = above;
       int bin = 8 * lane;
 #pragma unroll
       for (int k = 7; k >= 0; --k) {
         acc += loc[k];
-        if (acc >= (uint32_t)r) { bin = 8 * lane + k; break; }
+        if (acc >= rank) { bin = 8 * lane + k; break; }
       }
       bin = bin > 254 ? 254 : bin;  // ties at the maximum must still pass a strict compare
       const float guess = smin + (float)bin * __fdividef(smax - smin, 255.f);
-      sel[3] = __float_as_uint(guess);
       ValueBuckets later;
       later.set(guess, smax + (smax - guess));
-      vb_out[0] = later.lo;
-      vb_out[1] = later.scale;
+      if (which == 0) {
+        sel[3] = __float_as_uint(guess);
+        vb_out[0] = later.lo;
+        vb_out[1] = later.scale;
+      } else {
+        second[0] = guess;
+        second[1] = later.lo;
+        second[2] = later.scale;
+      }
     }
   }
   __syncthreads();

@@ -28,9 +28,6 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
   cg::cluster_group cluster = cg::this_cluster();
   const int csize = (int)cluster.num_blocks();
   const int crank = (int)cluster.block_rank();
-  // cluster launches only: one slot per other CTA of the cluster for its winners, then (count, guess key) per slot
-  unsigned long long *inbox = reinterpret_cast<unsigned long long *>(smem_raw + a.inbox_off);
-  int *inbox_meta = reinterpret_cast<int *>(inbox + (size_t)(csize - 1) * kSmallMaxM);
   const int tid = threadIdx.x, lane = tid & 31;
   const int Vt = a.vocab_total;
   const uint32_t ring_s = smem_u32(ring), full_s = smem_u32(&S.full[0]);
@@ -155,9 +152,8 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     // kernels_x86.cpp:509).  A NaN logit passes the test and is ordered below -inf by its key later.
     float thr = __int_as_float(0x7fc00000);
     bool booted = false;
-    float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
-    int second_rank = 0;                             // rank of a second, lower guess should the first one fail
     if (can_boot) {
+      float m1 = __int_as_float(0xff800000), m2 = m1;  // this thread's two largest sampled values
       for (int j = 0; j < kSampleTiles; ++j) {
         const int g = g0 + j;
         if (!mbar_wait_bounded(&S.full[g & (nst - 1)], (uint32_t)(g >> lg) & 1u)) failed = true;
@@ -174,7 +170,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
         }
       }
       for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;  // set-up of block_guess_threshold
-      if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
+      if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; S.second[0] = __int_as_float(0x7fc00000); }
       __syncthreads();  // the sample has been read by every thread; the penalty table is cleared
       if (!first_tiles_sample) {
         g0 += kSampleTiles;  // start the stream proper while the threshold is worked out (its tiles are fetched again)
@@ -190,10 +186,12 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       r = r < (lean ? kLeanMinRank : 16) ? (lean ? kLeanMinRank : 16) : r;
       booted = Mloc < Vt && r <= kThreads * 3 / 4;  // two maxima per thread hold the sample's best few dozen well enough
       if (booted) {
-        thr = block_guess_threshold(m1, m2, (int)r, S.hist, S.sel, S.vbp);  // NaN: no usable guess
+        // (with a second, lower guess at four times the rank for the case that the first one fails: the sample can
+        // mislead on sorted or clustered logits, and the exact stream may cost a select per chunk on such data)
+        const int r2 = 4 * r + 16 <= kThreads * 3 / 4 ? (int)(4 * r + 16) : 0;
+        thr = block_guess_threshold(m1, m2, (int)r, r2, S.hist, S.sel, S.vbp, S.second);  // NaN: no usable guess
         booted = thr == thr;
         have_vb = booted;
-        if (booted && 4 * r + 16 <= kThreads * 3 / 4) second_rank = (int)(4 * r + 16);
       }
     }
     QPB_STAMP(1);
@@ -427,6 +425,9 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
         n = min(S.cand_count, kCandCap);
         if (n > Mloc) { n = block_keep_top(S.cand, n, Mloc, S.hist, S.sel, &S.cand_count); guess = false; }
         const uint32_t gkey = guess ? f2key(thr) : 0u;
+        // the inbox: one slot per other CTA of the cluster for its winners, then (count, guess key) per slot
+        unsigned long long *inbox = reinterpret_cast<unsigned long long *>(smem_raw + a.inbox_off);
+        int *inbox_meta = reinterpret_cast<int *>(inbox + (size_t)(csize - 1) * kSmallMaxM);
         if (crank != 0) {
           unsigned long long *slot = cluster.map_shared_rank(inbox + (size_t)(crank - 1) * kSmallMaxM, 0);
           int *meta = cluster.map_shared_rank(inbox_meta + 2 * (crank - 1), 0);
@@ -480,15 +481,13 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       __syncthreads();
       booted = have_vb = hist_ok = false;
       thr = __int_as_float(0x7fc00000);
-      if (second_rank > 0) {
-        // The sample misled the first guess (sorted or clustered logits).  Before the exact stream, which can cost
-        // a select per chunk on such data, one more try with a threshold well down the sample.
+      const float thr2 = can_boot ? S.second[0] : __int_as_float(0x7fc00000);  // the second guess, if one is left
+      __syncthreads();
+      if (thr2 == thr2) {
+        thr = thr2;
+        booted = have_vb = true;
+        if (tid == 0) { S.vbp[0] = S.second[1]; S.vbp[1] = S.second[2]; S.second[0] = __int_as_float(0x7fc00000); }
         for (int i = tid; i < 256; i += kThreads) S.hist[i] = 0;
-        if (tid == 0) { S.sel[0] = 0xffffffffu; S.sel[1] = 0u; S.sel[3] = 0x7fc00000u; }
-        __syncthreads();
-        thr = block_guess_threshold(m1, m2, second_rank, S.hist, S.sel, S.vbp);
-        booted = have_vb = thr == thr;
-        second_rank = 0;
       }
       if (tid == 0) {
         S.cand_count = 0;
