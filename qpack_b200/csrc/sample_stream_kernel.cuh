@@ -243,12 +243,15 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
           const int cnt_before = S.cand_count;
           const uint32_t stage_s = ring_s + (uint32_t)st * (kTile * 4u);
           const uint32_t lane_s = stage_s + (uint32_t)tid * 16u;
-          uint32_t mask = 0;  // bit 4c + j: column c * kChunk + tid * 4 + j of the tile survives
-          mask_not_le<0>(lds_f4(lane_s), thr, mask);
-          mask_not_le<4>(lds_f4(lane_s + kThreads * 16u), thr, mask);
-          mask_not_le<8>(lds_f4(lane_s + kThreads * 32u), thr, mask);
-          mask_not_le<12>(lds_f4(lane_s + kThreads * 48u), thr, mask);
+          // bit 4c + j: column c * kChunk + tid * 4 + j of the tile survives (four short dependency chains, not one)
+          uint32_t mk0 = 0, mk1 = 0, mk2 = 0, mk3 = 0;
+          mask_not_le<0>(lds_f4(lane_s), thr, mk0);
+          mask_not_le<4>(lds_f4(lane_s + kThreads * 16u), thr, mk1);
+          mask_not_le<8>(lds_f4(lane_s + kThreads * 32u), thr, mk2);
+          mask_not_le<12>(lds_f4(lane_s + kThreads * 48u), thr, mk3);
+          uint32_t mask = (mk0 | mk1) | (mk2 | mk3);
           const uint32_t lanes = __ballot_sync(0xffffffffu, mask != 0u);
+          int level = 0;  // 1: the list has grown past the fast-mode mark, 2: past its capacity
           if (lanes != 0u) {
             // Same-address shared-memory atomics serialise and a warp scan is not free either: a warp with few
             // survivors lets each of those lanes reserve its own slots, a warp with many reserves once for all
@@ -275,10 +278,11 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
               put(pos, lds_f32(stage_s + (uint32_t)off * 4u), a.id_offset + tbase + off);
               ++pos;
             }
+            if (nacc) level = pos > kCandCap ? 3 : (pos > kCandHighFast ? 1 : 0);
           }
-          __syncthreads();  // stage consumed by every thread; candidate count settled
-          const int cnt = S.cand_count;
-          if (cnt > kCandCap) {
+          // stage consumed by every thread; candidate count settled; the highest slot taken tells how full the list is
+          const int fill = __syncthreads_or(level);
+          if (fill & 2) {
             // more survivors than the list holds: forget this tile's, scan it again chunk by chunk
             __syncthreads();
             if (tid == 0) S.cand_count = cnt_before;
@@ -288,7 +292,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
             continue;
           }
           if (tid == 0) issue(t + nst, g + nst);
-          if (cnt > kCandHighFast && cnt > Mloc) shrink();
+          if (fill && S.cand_count > Mloc) shrink();
           ++t;
           continue;
         }
