@@ -29,7 +29,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 VOCAB = 151936
-NCU_DRAM_BYTES_PER_ROW = 624_500  # (365.62 MB read + 4.08 MB written) / 592 rows, 128-thread build; algorithmic: 4 * V = 607_744
+NCU_DRAM_BYTES_PER_ROW = 631_340  # (368.10 MB read + 5.65 MB written) / 592 rows, 128-thread build; algorithmic: 4 * V = 607_744
 FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
 
 
