@@ -567,32 +567,22 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
   const int per = (nK + 31) >> 5;  // consecutive entries per lane
   const int j0 = min(nK, lane * per), j1 = min(nK, j0 + per);
   const bool exact_sums = ev[nK - 1] >= 0x1p-20f;  // ev is descending
-  double *qd = reinterpret_cast<double *>(sorted + 512);  // nK <= 500 entries of sorted are in use, 512 more follow
-  double sum = 0.0;
-  if (exact_sums) {
-#pragma unroll 1
-    for (int j = j0; j < j1; ++j) sum += (double)ev[j];
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  } else {
-#pragma unroll 4
-    for (int j = 0; j < nK; ++j) sum += (double)ev[j];
-  }
-  if (clk) clk[13] = clock64();
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
   const bool use_minp = p.min_p > 0.f;
   const double top_p = (double)p.top_p;
-  // lane-local pass: quotients, their sum, entries that pass min-p (a prefix: ev is descending)
-  double lt = 0.0;
+  // lane-local pass: sum of the lane's numerators, entries that pass min-p (a prefix: ev is descending)
+  double le = 0.0;
   int passes = 0;
 #pragma unroll 1
   for (int j = j0; j < j1; ++j) {
     const float e = ev[j];
-    const double q = __ddiv_rn((double)e, sum);
-    qd[j] = q;
-    lt += q;
+    le += (double)e;
     passes += (use_minp && e < minp_thr) ? 0 : 1;
   }
+  double sum = le;  // exactly the reference's sum when exact_sums, else within rounding of it
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (clk) clk[13] = clock64();
   auto warp_exclusive = [&](double v) {  // sum of v over lower lanes
     double incl = v;
 #pragma unroll
@@ -605,24 +595,33 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
   };
   int keep;
   {
-    double c = warp_exclusive(lt);
+    // The reference adds up e_i / sum and compares with top_p (sampler.cpp:50-51); that running sum equals the
+    // prefix sum of the e_i over `sum` within 1e-13 relative, so away from equality the prefix sums of the
+    // numerators can be compared with top_p * sum and no division is needed.
+    const double target = top_p * sum, margin = kEps * sum;
+    double c = warp_exclusive(le);
     int below = 0;
-    bool amb = false;
+    bool amb = !(sum > 0.0 && sum < 1e300);  // NaN or infinite numerators: whatever the reference's walk does
 #pragma unroll 1
     for (int j = j0; j < j1; ++j) {
-      c += qd[j];
-      below += (c < top_p) ? 1 : 0;
-      amb |= (j < nK - 1) && (fabs(c - top_p) <= kEps);  // at the last entry both outcomes keep everything
+      c += (double)ev[j];
+      below += (c < target) ? 1 : 0;
+      amb |= (j < nK - 1) && (fabs(c - target) <= margin);  // at the last entry both outcomes keep everything
     }
     const int first_fail = __reduce_add_sync(0xffffffffu, passes);  // == nK: nothing fails
     int first_top = __reduce_add_sync(0xffffffffu, below);          // == nK: never reached
-    if (__any_sync(0xffffffffu, amb)) {  // sampler.cpp:48-52 entry by entry
-      __syncwarp();
+    if (__any_sync(0xffffffffu, amb)) {  // sampler.cpp:46-52 entry by entry
+      double s = sum;
+      if (!exact_sums) {
+        s = 0.0;
+#pragma unroll 1
+        for (int j = 0; j < nK; ++j) s += (double)ev[j];
+      }
       double cum = 0.0;
       first_top = nK;
 #pragma unroll 1
       for (int j = 0; j < nK; ++j) {
-        cum += qd[j];
+        cum += __ddiv_rn((double)ev[j], s);
         if (cum >= top_p) { first_top = j; break; }
       }
     }
