@@ -560,9 +560,9 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
   //    every partial sum in any order is a multiple of 2^-43 below 2^10, hence exact in double, so a tree gives
   //    the sequential result bit for bit;
   //  * running sums that are only compared (cumulative probability against top_p, the draw against the
-  //    cumulative distribution): prefix sums in another order differ from the sequential ones by less than
-  //    1e-13, so a comparison that is not within 1e-12 of equality has the same outcome.
-  // Anything else (tiny numerators, a comparison within 1e-12) takes the sequential walk.
+  //    cumulative distribution): both are prefix sums of the numerators over a constant up to a known rounding
+  //    bound, so a comparison that is not within that bound of equality has the same outcome.
+  // Anything else (tiny numerators, a comparison too close to call) takes the sequential walk.
   constexpr double kEps = 1e-12;
   const int per = (nK + 31) >> 5;  // consecutive entries per lane
   const int j0 = min(nK, lane * per), j1 = min(nK, j0 + per);
@@ -593,13 +593,14 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
     const double prev = __shfl_up_sync(0xffffffffu, incl, 1);
     return lane == 0 ? 0.0 : prev;
   };
+  const double base_e = warp_exclusive(le);  // sum of the numerators before this lane's entries
   int keep;
   {
     // The reference adds up e_i / sum and compares with top_p (sampler.cpp:50-51); that running sum equals the
     // prefix sum of the e_i over `sum` within 1e-13 relative, so away from equality the prefix sums of the
     // numerators can be compared with top_p * sum and no division is needed.
     const double target = top_p * sum, margin = kEps * sum;
-    double c = warp_exclusive(le);
+    double c = base_e;
     int below = 0;
     bool amb = !(sum > 0.0 && sum < 1e300);  // NaN or infinite numerators: whatever the reference's walk does
 #pragma unroll 1
@@ -642,13 +643,8 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
 #pragma unroll 4
     for (int j = 0; j < keep; ++j) tot += (double)ev[j];
   }
-  double pl = 0.0;
 #pragma unroll 1
-  for (int j = j0; j < k1; ++j) {  // sampler.cpp:55
-    const float pj = __double2float_rn(__ddiv_rn((double)ev[j], tot));
-    pv[j] = pj;
-    pl += (double)pj;
-  }
+  for (int j = j0; j < k1; ++j) pv[j] = __double2float_rn(__ddiv_rn((double)ev[j], tot));  // sampler.cpp:55
   __syncwarp();
   if (clk) clk[3] = clock64();
   // draw (sampler.cpp:58-63): the first entry at which the variate, less the probabilities so far, is <= 0
@@ -658,14 +654,17 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
     if (lane == 0) w = mt_commit(rng, a.rng_state + (size_t)row * MT_N, a.rng_drawn + row);
     w = __shfl_sync(0xffffffffu, w, 0);
     const double r = word_to_uniform(w);
-    double c = warp_exclusive(pl);
+    // The probabilities are e_i / tot rounded to float, so their running sum lies within 6e-8 of the numerators'
+    // prefix sum over tot: away from that, comparing the prefix sums with r * tot gives the reference's outcome.
+    const double target = r * tot, margin = 2e-7 * tot;
+    double c = base_e;
     int below = 0;
-    bool amb = false;
+    bool amb = !(tot > 0.0 && tot < 1e300);
 #pragma unroll 1
     for (int j = j0; j < k1; ++j) {
-      c += (double)pv[j];
-      below += (c < r) ? 1 : 0;
-      amb |= (j < keep - 1) && (fabs(c - r) <= kEps);  // the last entry is picked whatever is left
+      c += (double)ev[j];
+      below += (c < target) ? 1 : 0;
+      amb |= (j < keep - 1) && (fabs(c - target) <= margin);  // the last entry is picked whatever is left
     }
     pick = __reduce_add_sync(0xffffffffu, below);
     pick = pick < keep - 1 ? pick : keep - 1;
