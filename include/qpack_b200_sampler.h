@@ -147,6 +147,11 @@ QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
  * With 128 threads a cluster holds at most 4 CTAs. */
 QPB_API int qpb_sampler_set_stream_config(qpb_sampler *s, int threads, int log2_stages);
 
+/* Test switch (no counterpart in the reference).  Bit 0: every order-sensitive step of the finish and of the
+ * verification walks (double sums, cumulative comparisons) takes its sequential fallback, which normally only runs
+ * when a comparison is too close to call; results must not change. */
+QPB_API int qpb_sampler_set_debug(qpb_sampler *s, int flags);
+
 /* Row pieces: the tiles of all rows of a call laid end to end and dealt out in equal runs to as many CTAs as fit on
  * the GPU, rows that straddle two CTAs merged through device scratch (allocated on first use).  mode 0 (default):
  * only when whole rows would leave the last wave of CTAs less than a quarter full; 1: always; -1: never. */

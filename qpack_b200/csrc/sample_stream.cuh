@@ -67,6 +67,7 @@ struct StreamArgs {
   int pen_slots;           // penalty hash slots (power of two)
   int log2_stages;         // ring depth = 1 << log2_stages (1 .. 3)
   int inbox_off;           // cluster launches: byte offset of the leader's inbox in dynamic shared memory
+  int debug_flags;         // bit 0: take the sequential fallback of every order-sensitive step (tests)
   // Row pieces (one CTA per cluster only).  units_per_cta > 0: the rows of this launch, cut into tiles of kTile
   // columns and laid end to end, are dealt out in equal runs of units_per_cta tiles to the CTAs of the grid; a row
   // that straddles CTAs is sampled in pieces, each piece leaves its best candidates in piece_cand, and the CTA
@@ -566,7 +567,7 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
   constexpr double kEps = 1e-12;
   const int per = (nK + 31) >> 5;  // consecutive entries per lane
   const int j0 = min(nK, lane * per), j1 = min(nK, j0 + per);
-  const bool exact_sums = ev[nK - 1] >= 0x1p-20f;  // ev is descending
+  const bool exact_sums = ev[nK - 1] >= 0x1p-20f && !(a.debug_flags & 1);  // ev is descending
   const float minp_thr = __fmul_rn(p.min_p, ev[0]);
   const bool use_minp = p.min_p > 0.f;
   const double top_p = (double)p.top_p;
@@ -602,7 +603,7 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
     const double target = top_p * sum, margin = kEps * sum;
     double c = base_e;
     int below = 0;
-    bool amb = !(sum > 0.0 && sum < 1e300);  // NaN or infinite numerators: whatever the reference's walk does
+    bool amb = !(sum > 0.0 && sum < 1e300) || (a.debug_flags & 1);  // NaN or infinite numerators: whatever the reference's walk does
 #pragma unroll 1
     for (int j = j0; j < j1; ++j) {
       c += (double)ev[j];
@@ -659,7 +660,7 @@ static __device__ void finish_row(const StreamArgs &a, int row, const RowParams 
     const double target = r * tot, margin = 2e-7 * tot;
     double c = base_e;
     int below = 0;
-    bool amb = !(tot > 0.0 && tot < 1e300);
+    bool amb = !(tot > 0.0 && tot < 1e300) || (a.debug_flags & 1);
 #pragma unroll 1
     for (int j = j0; j < k1; ++j) {
       c += (double)ev[j];

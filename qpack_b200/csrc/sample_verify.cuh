@@ -28,6 +28,7 @@ struct VerifyArgs {
   int *accepted;            // [n_chains] proposals accepted
   int *next;                // [n_chains] the token that follows them: the replacement, or the draw of the next row
   int *status;
+  int debug_flags;          // bit 0: take the sequential walk always (tests)
 };
 
 constexpr int kVerifyWarps = 4;  // chains per CTA
@@ -49,12 +50,13 @@ __device__ __forceinline__ double verify_uniform(unsigned long long *mt, unsigne
 // the first entry at which the remainder is <= 0, else the last entry.  Here 32 entries at a time are compared
 // through a warp prefix sum; a comparison within 1e-9 of equality (the two orders of addition differ by far less)
 // sends the whole walk down the sequential path instead.
-__device__ int verify_walk(const int *ids, const float *p, int n, int skip, bool divide, float denom, double r, int lane) {
+__device__ int verify_walk(const int *ids, const float *p, int n, int skip, bool divide, float denom, double r, int lane,
+                           bool force_sequential) {
   constexpr double kEps = 1e-9;
   double carry = 0.0;
   int last_id = -1;
-  bool ambiguous = false;
-  for (int base = 0; base < n; base += 32) {
+  bool ambiguous = force_sequential;
+  for (int base = 0; base < n && !ambiguous; base += 32) {
     const int j = base + lane;
     int id = -1;
     double q = 0.0;
@@ -145,7 +147,7 @@ __global__ void __launch_bounds__(32 * kVerifyWarps) verify_chains_kernel(const 
       next = other;
     } else {
       const double r = verify_uniform(mt, drawn, lane);
-      next = verify_walk(ids, pr, n, token, true, __fsub_rn(1.f, p), r, lane);
+      next = verify_walk(ids, pr, n, token, true, __fsub_rn(1.f, p), r, lane, a.debug_flags & 1);
     }
     break;
   }
@@ -157,7 +159,7 @@ __global__ void __launch_bounds__(32 * kVerifyWarps) verify_chains_kernel(const 
     int n = a.dist_count[row];
     if (n > a.max_out) { if (lane == 0) atomicOr(a.status, ST_CAPACITY); n = a.max_out; }
     if (n <= 1) next = n == 1 ? ids[0] : -1;
-    else next = verify_walk(ids, pr, n, -1, false, 1.f, verify_uniform(mt, drawn, lane), lane);
+    else next = verify_walk(ids, pr, n, -1, false, 1.f, verify_uniform(mt, drawn, lane), lane, a.debug_flags & 1);
   }
   if (lane == 0) {
     a.accepted[chain] = acc;

@@ -38,6 +38,7 @@ struct qpb_sampler {
   bool attr_done[2][3][2] = {};  // streaming kernel instantiations: [block size][mode][timed]
   bool whole_attr_done = false;
   int force_threads = 0, force_log2_stages = 0;  // 0: chosen per launch
+  int debug_flags = 0;
   int64_t launches = 0;
   // staging for the host-buffer entry point
   float *d_stage_logits = nullptr;
@@ -305,6 +306,7 @@ void fill_common(qpb_sampler *s, const Inputs &in, StreamArgs &a) {
   a.hist_len = in.d_hist_len;
   a.hist_len_all = in.d_history ? in.hist_len_all : 0;
   a.append = in.append ? 1 : 0;
+  a.debug_flags = s->debug_flags;
   a.rng_state = s->d_rng;
   a.rng_drawn = s->d_drawn;
   a.status = s->d_status;
@@ -672,9 +674,16 @@ int qpb_sampler_verify_chains(qpb_sampler *s, const int32_t *d_dist_ids, const f
   a.accepted = d_accepted;
   a.next = d_next;
   a.status = s->d_status;
+  a.debug_flags = s->debug_flags;
   verify_chains_kernel<<<(n_chains + kVerifyWarps - 1) / kVerifyWarps, 32 * kVerifyWarps, 0, (cudaStream_t)stream>>>(a);
   QPB_CUDA(s, cudaGetLastError());
   s->launches++;
+  return QPB_OK;
+}
+
+int qpb_sampler_set_debug(qpb_sampler *s, int flags) {
+  if (!s) return QPB_ERR_INVALID;
+  s->debug_flags = flags;
   return QPB_OK;
 }
 

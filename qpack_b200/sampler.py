@@ -83,6 +83,10 @@ class BatchSampler:
         """Threads per CTA (128 / 256) and log2 ring depth (1..3) of the streaming kernel; 0 = chosen per launch."""
         self._ck(self._lib.qpb_sampler_set_stream_config(self._h, int(threads), int(log2_stages)))
 
+    def set_debug(self, flags: int):
+        """Test switch: bit 0 forces the sequential fallback of every order-sensitive step."""
+        self._ck(self._lib.qpb_sampler_set_debug(self._h, int(flags)))
+
     def set_cluster(self, cluster: int):
         self._ck(self._lib.qpb_sampler_set_cluster(self._h, int(cluster)))
 

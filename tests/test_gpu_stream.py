@@ -15,12 +15,13 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def run_device(params, logits, hist=None, hist_len=None, max_out=64, cluster=0, draw=True, config=(0, 0)):
+def run_device(params, logits, hist=None, hist_len=None, max_out=64, cluster=0, draw=True, config=(0, 0), debug=0):
     B = logits.shape[0]
     bs = BatchSampler(B, 0)
     bs.set_params(params)
     bs.set_cluster(cluster)
     bs.set_stream_config(*config)
+    bs.set_debug(debug)
     d_logits = torch.from_numpy(np.ascontiguousarray(logits)).to(DEV)
     d_hist = torch.from_numpy(np.ascontiguousarray(hist)).to(DEV) if hist is not None else None
     d_hl = torch.from_numpy(np.ascontiguousarray(hist_len)).to(DEV) if hist_len is not None else None
@@ -203,6 +204,28 @@ def test_adversarial_rows(config):
             got = run_device(params, logits, hist, None, max_out=256, cluster=cluster, config=config)
             rep = compare_rows(*got, exp)
             assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (top_k, rp, cluster, rep)
+
+
+@pytest.mark.parametrize("name", ["serving", "mixed", "loop_row"])
+def test_sequential_fallbacks_agree(name):
+    """The finish replaces the reference's entry-by-entry double arithmetic by prefix sums wherever a comparison is
+    not too close to call; the switch forces the entry-by-entry fallback everywhere: same results, bit for bit."""
+    if name == "loop_row":
+        params, hist0 = synth.single_row_loop()
+        logits = np.concatenate([synth.single_row_step(i) for i in range(24)], 0)
+        params = np.repeat(params, 24)
+        params["seed"] = np.arange(24) + 77
+        hist = np.repeat(hist0[None, :], 24, axis=0).astype(np.int32)
+        hl = None
+    else:
+        wl = {"serving": synth.serving_batch, "mixed": synth.mixed_batch}[name](rows=48)
+        wl.params["top_k"][wl.params["top_k"] == 0] = 200
+        params, logits, hist, hl = wl.params, wl.logits, wl.history, wl.hist_len
+    exp = Oracle.sample_rows(params, logits, hist, hl, max_out=256)
+    for cluster in (1, 4):
+        got = run_device(params, logits, hist, hl, max_out=256, cluster=cluster, debug=1)
+        rep = compare_rows(*got, exp)
+        assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, (cluster, rep)
 
 
 @pytest.mark.parametrize("rows", [7, 96, 700])

@@ -45,8 +45,9 @@ def _replay(cls, params_c, logits_c, hist_c, base, proposals_c, k_c):
     return acc, nxt, drawn
 
 
+@pytest.mark.parametrize("debug", [0, 1])
 @pytest.mark.parametrize("V", [4099, 151936])
-def test_verify_chains_match_the_reference_loop(V):
+def test_verify_chains_match_the_reference_loop(V, debug):
     rng = np.random.default_rng(21)
     n_chains, k = 40, 5
     base, logits, hist, params = _chains(n_chains, k, V, rng)
@@ -72,6 +73,7 @@ def test_verify_chains_match_the_reference_loop(V):
     row_params = np.repeat(params, k + 1)
     bs = BatchSampler(rows, 0)
     bs.set_params(row_params)
+    bs.set_debug(debug)  # 1: every walk takes its sequential fallback
     d_x = torch.from_numpy(logits).to(DEV)
     d_h = torch.from_numpy(np.repeat(hist, k + 1, axis=0)).to(DEV)
     hl = (base + 1 + np.tile(np.arange(k + 1), n_chains)).astype(np.int32)
