@@ -67,6 +67,11 @@ QPB_API int qpb_sampler_destroy(qpb_sampler *s);
  * single sampler).  Re-seeds every row's MT19937-64 stream.  Synchronous. */
 QPB_API int qpb_sampler_set_params(qpb_sampler *s, const qpb_sampler_params *params, int n);
 
+/* A new request takes over one row: its parameters, and a random stream seeded afresh from params->seed (a new
+ * qp::Sampler for the request, tools/qpack-server.cpp:127), while the other rows keep theirs.  Ordered on `stream`
+ * with the sampling calls.  Needs an earlier qpb_sampler_set_params with one block or with max_rows blocks. */
+QPB_API int qpb_sampler_set_row_params(qpb_sampler *s, int row, const qpb_sampler_params *params, void *stream);
+
 /* Replaces qp::Sampler::sample (engine.h:30) for n_rows rows: d_out_ids[r] = sampled token of row r.
  * d_logits: [n_rows][row_stride] f32, vocab <= row_stride.  d_history: [n_rows][hist_stride] token ids (may be
  * NULL); d_hist_len[r] (<= hist_stride) entries of row r are visible, or hist_len_all for every row when

@@ -477,6 +477,35 @@ int qpb_sampler_set_params(qpb_sampler *s, const qpb_sampler_params *params, int
   return QPB_OK;
 }
 
+int qpb_sampler_set_row_params(qpb_sampler *s, int row, const qpb_sampler_params *params, void *stream) {
+  if (!s) return QPB_ERR_INVALID;
+  if (!params || row < 0 || row >= s->max_rows) return fail(s, QPB_ERR_INVALID, "params null or row outside [0, max_rows)");
+  if (s->n_params != 1 && s->n_params != s->max_rows)
+    return fail(s, QPB_ERR_INVALID, "qpb_sampler_set_params must have set one block, or one per row, first");
+  DeviceGuard g(s->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (s->n_params == 1) {  // from one shared block to one block per row (the rows keep their random streams)
+    s->h_params.resize((size_t)s->max_rows, s->h_params[0]);
+    s->n_params = s->max_rows;
+    QPB_CUDA(s, cudaMemcpyAsync(s->d_params, s->h_params.data(), sizeof(RowParams) * s->max_rows, cudaMemcpyHostToDevice, st));
+    QPB_CUDA(s, cudaStreamSynchronize(st));
+  }
+  s->h_params[(size_t)row] = *params;
+  s->routed_rows = -1;
+  uint64_t seed = params->seed;
+  if (seed == 0) {  // non-deterministic, as std::random_device{}() in the reference
+    std::random_device rd;
+    seed = ((uint64_t)rd() << 32) ^ rd();
+  }
+  uint64_t mt[MT_N];
+  mt_seed_host(seed, mt);
+  // (copies from pageable memory return once the source has been staged, so the stack buffers may go out of scope)
+  QPB_CUDA(s, cudaMemcpyAsync(s->d_params + row, params, sizeof(RowParams), cudaMemcpyHostToDevice, st));
+  QPB_CUDA(s, cudaMemcpyAsync(s->d_rng + (size_t)row * MT_N, mt, sizeof(mt), cudaMemcpyHostToDevice, st));
+  QPB_CUDA(s, cudaMemsetAsync(s->d_drawn + row, 0, sizeof(unsigned int), st));
+  return QPB_OK;
+}
+
 int qpb_sampler_sample_batch(qpb_sampler *s, const float *d_logits, int64_t row_stride, int n_rows, int vocab,
                              const int32_t *d_history, int64_t hist_stride, const int32_t *d_hist_len,
                              int hist_len_all, int32_t *d_out_ids, void *stream) {

@@ -83,6 +83,11 @@ class BatchSampler:
         """Threads per CTA (128 / 256) and log2 ring depth (1..3) of the streaming kernel; 0 = chosen per launch."""
         self._ck(self._lib.qpb_sampler_set_stream_config(self._h, int(threads), int(log2_stages)))
 
+    def set_row_params(self, row: int, params: "SamplerParams", stream=None):
+        """A new request takes over one row: its parameters and a fresh random stream; other rows are untouched."""
+        arr = params.to_array() if isinstance(params, SamplerParams) else np.ascontiguousarray(params, dtype=PARAMS_DTYPE)
+        self._ck(self._lib.qpb_sampler_set_row_params(self._h, int(row), arr.ctypes.data, self._stream(stream)))
+
     def set_debug(self, flags: int):
         """Test switch: bit 0 forces the sequential fallback of every order-sensitive step."""
         self._ck(self._lib.qpb_sampler_set_debug(self._h, int(flags)))
