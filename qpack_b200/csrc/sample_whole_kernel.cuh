@@ -150,10 +150,13 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
     // ---- top-p (sampler.cpp:51): first position whose running sum of e / sum reaches top_p ----
     unsigned long long keep_b = in_count;
     if (p.top_p < 1.f) {
+      // Masses are the numerators themselves in 2^-44 fixed point (exact for numerators >= 2^-20, the others lose
+      // less than 2^-44 each: 1e-8 of the top numerator over a whole row), compared with top_p * sum: no division
+      // per column and pass, and sums that do not depend on the order of the additions.
       const double tp = (double)p.top_p;
-      const unsigned long long target = tp <= 0.0 ? 1ULL : __double2ull_ru(tp * 0x1p62);
+      const unsigned long long target = tp <= 0.0 ? 1ULL : __double2ull_ru(tp * sum * 0x1p44);
       const MassPos mp = cluster_mass_find(c, target, [&](int i, uint32_t k) -> unsigned long long {
-        return __double2ull_rz(__ddiv_rn((double)e_of(i, k), sum) * 0x1p62);
+        return __float2ull_rz(e_of(i, k) * 0x1p44f);
       });
       if (mp.found) keep_b = mp.pos;
     }
@@ -176,10 +179,11 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
         // the word travels from the leader to everybody through an exchange slot
         w = cluster_sum_u64(c, leader0 ? w : 0ULL);
         const double u = word_to_uniform(w);
-        const unsigned long long target = __double2ull_ru(u * 0x1p62);
+        // the same masses against u * tot: the probabilities are the numerators over tot rounded to float, so their
+        // running sum lies within 6e-8 of this one (the tolerance on a draw next to a boundary is 1e-6)
+        const unsigned long long target = __double2ull_ru(u * tot * 0x1p44);
         const MassPos mp = cluster_mass_find(c, target, [&](int i, uint32_t k) -> unsigned long long {
-          const float pr = __double2float_rn(__ddiv_rn((double)e_of(i, k), tot));
-          return __double2ull_rz((double)pr * 0x1p62);
+          return __float2ull_rz(e_of(i, k) * 0x1p44f);
         });
         if (mp.found) {
           picked = cluster_id_of_jth(c, mp.key, mp.j, s0);

@@ -13,18 +13,38 @@ __device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, 
   WholeSmem *S = c.S;
   if (threadIdx.x < 256) {
     S->hist[threadIdx.x] = 0;
-    if (WEIGHTED) S->whist[threadIdx.x] = 0ULL;
+    if (WEIGHTED) { S->whist[0][threadIdx.x] = 0u; S->whist[1][threadIdx.x] = 0u; S->whist[2][threadIdx.x] = 0u; S->whist[3][threadIdx.x] = 0u; }
   }
   __syncthreads();
   const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
+  // Neighbouring columns mostly share their digit (in the first pass nearly the whole row does: sign and upper
+  // exponent bits), so a thread adds up runs of equal digits in registers and touches the histogram once per run.
+  uint32_t run_d = 0xffffffffu, run_n = 0;
+  unsigned long long run_w = 0;
+  auto flush = [&](uint32_t d, uint32_t n, unsigned long long w) {
+    atomicAdd(&S->hist[d], n);
+    if (WEIGHTED) {  // 64-bit shared-memory adds are slow under contention: four 32-bit adds of 16-bit limbs instead
+      atomicAdd(&S->whist[0][d], (uint32_t)(w & 0xffffULL));
+      atomicAdd(&S->whist[1][d], (uint32_t)((w >> 16) & 0xffffULL));
+      atomicAdd(&S->whist[2][d], (uint32_t)((w >> 32) & 0xffffULL));
+      atomicAdd(&S->whist[3][d], (uint32_t)(w >> 48));
+    }
+  };
   for (int i = i0; i < i1; ++i) {
     const uint32_t k = c.keys[i];
     if (k != kExcl && (k & mask) == prefix) {
       const uint32_t d = (k >> shift) & 255u;
-      atomicAdd(&S->hist[d], 1u);
-      if (WEIGHTED) atomicAdd(&S->whist[d], wf(i, k));
+      if (d != run_d) {
+        if (run_n) flush(run_d, run_n, run_w);
+        run_d = d;
+        run_n = 0;
+        run_w = 0;
+      }
+      ++run_n;
+      if (WEIGHTED) run_w += wf(i, k);
     }
   }
+  if (run_n) flush(run_d, run_n, run_w);
   cooperative_groups::this_cluster().sync();  // every CTA's histogram is complete
   if (threadIdx.x < 256) {
     uint32_t t = 0;
@@ -32,7 +52,9 @@ __device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, 
     for (int r = 0; r < c.csize; ++r) {
       const WholeSmem *R = cooperative_groups::this_cluster().map_shared_rank(S, r);
       t += R->hist[threadIdx.x];
-      if (WEIGHTED) tw += R->whist[threadIdx.x];
+      if (WEIGHTED)
+        tw += (unsigned long long)R->whist[0][threadIdx.x] + ((unsigned long long)R->whist[1][threadIdx.x] << 16) +
+              ((unsigned long long)R->whist[2][threadIdx.x] << 32) + ((unsigned long long)R->whist[3][threadIdx.x] << 48);
     }
     S->thist[threadIdx.x] = t;
     if (WEIGHTED) S->twhist[threadIdx.x] = tw;
@@ -120,7 +142,7 @@ struct MassPos {
 
 // First position of the row ordered by (key descending, index ascending) whose running mass reaches `target`
 // (sampler.cpp:49-52 with mass = e / sum and target = top_p; sampler.cpp:60-61 with mass = p and target = u).
-// Masses are 2^-62 fixed point so that the histogram sums do not depend on the order of the additions.
+// Masses are integers (fixed point) so that the histogram sums do not depend on the order of the additions.
 template <class WeightFn>
 __device__ MassPos cluster_mass_find(WholeCtx &c, unsigned long long target, WeightFn wf) {
   WholeSmem *S = c.S;
