@@ -137,18 +137,21 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
     // ---- min-p (sampler.cpp:50): numerators fall along the order, so the columns that pass form a prefix ----
     const float e0 = expf_libm(__fdiv_rn(__fsub_rn(mx, mx), T), S.exp_tab);
     unsigned long long keep_a = in_count;
+    const float minp_thr = __fmul_rn(p.min_p, e0);
+    bool minp_none = false;  // nothing passes min-p: the best column stays (sampler.cpp:50, keep = max(i, 1))
     if (p.min_p > 0.f) {
-      const float thr = __fmul_rn(p.min_p, e0);
+      const float thr = minp_thr;
       int pass = 0;
       for (int i = i0; i < i1; ++i) {
         const uint32_t k = keys[i];
         if (k != kExcl && !(e_of(i, k) < thr)) ++pass;
       }
       keep_a = cluster_sum_u64(c, (unsigned long long)block_sum_int(c, pass));
-      if (keep_a < 1ULL) keep_a = 1ULL;
+      if (keep_a < 1ULL) { keep_a = 1ULL; minp_none = true; }
     }
     // ---- top-p (sampler.cpp:51): first position whose running sum of e / sum reaches top_p ----
     unsigned long long keep_b = in_count;
+    MassPos cut = {false, 0u, 0ULL, 0ULL};
     if (p.top_p < 1.f) {
       // Masses are the numerators themselves in 2^-44 fixed point (exact for numerators >= 2^-20, the others lose
       // less than 2^-44 each: 1e-8 of the top numerator over a whole row), compared with top_p * sum: no division
@@ -158,10 +161,31 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
       const MassPos mp = cluster_mass_find(c, target, [&](int i, uint32_t k) -> unsigned long long {
         return __float2ull_rz(e_of(i, k) * 0x1p44f);
       });
-      if (mp.found) keep_b = mp.pos;
+      if (mp.found) { keep_b = mp.pos; cut = mp; }
     }
     keep = keep_a < keep_b ? keep_a : keep_b;
-    if (keep < in_count) cluster_keep_top(c, keep);
+    if (keep < in_count) {
+      // Both cuts are known by value, so no count descent is needed: min-p keeps the columns whose numerator reaches
+      // its threshold, top-p keeps everything above the key at the crossing and the first j columns of that key.
+      if (keep_a <= keep_b && !minp_none) {
+        for (int i = i0; i < i1; ++i) {
+          const uint32_t k = keys[i];
+          if (k != kExcl && e_of(i, k) < minp_thr) keys[i] = kExcl;
+        }
+        __syncthreads();
+      } else if (keep_b < keep_a && cut.found) {
+        long long rank = ordered_rank_of_equal(c, cut.key);
+        for (int i = i0; i < i1; ++i) {
+          const uint32_t k = keys[i];
+          if (k == kExcl) continue;
+          if (k < cut.key) keys[i] = kExcl;
+          else if (k == cut.key) { if ((unsigned long long)rank >= cut.j) keys[i] = kExcl; ++rank; }
+        }
+        __syncthreads();
+      } else {
+        cluster_keep_top(c, keep);
+      }
+    }
     // ---- renormalise (sampler.cpp:54-55) ----
     part = 0.0;
     for (int i = i0; i < i1; ++i) {
