@@ -274,6 +274,12 @@ def run_ours(args, rank, world, local_rank):
             extra["sweep"] = sweep
         bs1.close()
 
+    # ---- vocabulary-sharded step (config 5), N > 1 only: latency-bound, reported by phase ----
+    if dist is not None:
+        sh = bench_vocab_sharded(torch, dist, dev, local_rank, rank, world)
+        if rank == 0:
+            extra["vocab_sharded"] = sh
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         bytes_per_launch = rows * 4 * VOCAB
@@ -304,6 +310,50 @@ def run_ours(args, rank, world, local_rank):
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
+    """Config 5 over the ranks of this run: 128 rows, V = 151936 split into contiguous column shards, local top-64
+    per shard -> one all-gather -> merge, filter and draw.  Device time per phase (CUDA events on the current
+    stream, max over ranks); every rank must end up with the same ids."""
+    from qpack_b200 import synth
+    from qpack_b200.distributed import gather_candidates, vocab_shard
+    from qpack_b200.sampler import BatchSampler
+
+    wl = synth.sharded_batch(rows=128, vocab=VOCAB)
+    c0, c1 = vocab_shard(VOCAB, world, rank)
+    per_max = max(vocab_shard(VOCAB, world, r)[1] - vocab_shard(VOCAB, world, r)[0] for r in range(world))
+    x = torch.from_numpy(np.ascontiguousarray(wl.logits[:, c0:c1])).to(dev)
+    bs = BatchSampler(128, local_rank)
+    bs.set_params(wl.params)
+    slots = bs.cand_slots(VOCAB, per_max)
+    stream = torch.cuda.current_stream(dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    acc = np.zeros(3)
+    ids = None
+    for it in range(iters + 3):
+        ev[0].record(stream)
+        local = bs.local_candidates(x, VOCAB, c0, slots)
+        ev[1].record(stream)
+        allc = gather_candidates(local)
+        ev[2].record(stream)
+        ids = bs.merge_sample(allc, VOCAB)
+        ev[3].record(stream)
+        torch.cuda.synchronize(dev)
+        if it >= 3:
+            acc += [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(3)]
+    bs.check()
+    bs.close()
+    t = torch.tensor(acc / iters, dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    same = ids.to(torch.int64).clone()
+    dist.broadcast(same, src=0)
+    agree = torch.tensor([int(torch.equal(same, ids.to(torch.int64)))], device=dev)
+    dist.all_reduce(agree, op=dist.ReduceOp.MIN)
+    us = [float(v) for v in t]
+    return {"rows": 128, "vocab": VOCAB, "shards": world, "local_topk_us": round(us[0], 1), "all_gather_us": round(us[1], 1),
+            "merge_draw_us": round(us[2], 1), "rows_per_s": round(128 / (sum(us) * 1e-6)),
+            "all_gather_bytes_sent_per_rank": int(128 * slots * 8), "ranks_agree": bool(int(agree.item()))}
 
 
 def wl_logits_np(pinned):
