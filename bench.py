@@ -342,8 +342,32 @@ def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
         torch.cuda.synchronize(dev)
         if it >= 3:
             acc += [ev[i].elapsed_time(ev[i + 1]) * 1e3 for i in range(3)]
+    # the same step, ten times over, captured in one CUDA graph (kernel -> all-gather -> kernel, no host in between)
+    graph_us = None
+    try:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(stream)
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(10):
+                    ids_g = bs.merge_sample(gather_candidates(bs.local_candidates(x, VOCAB, c0, slots)), VOCAB)
+            g.replay()
+            side.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            g.replay()
+            e1.record(side)
+            side.synchronize()
+            graph_us = e0.elapsed_time(e1) * 1e3 / 10
+    except Exception as exc:  # capture of the collective is not available: the per-phase numbers stand alone
+        graph_us = None
+        sys.stderr.write(f"vocab-sharded graph capture skipped: {exc}\n")
     bs.check()
     bs.close()
+    gt = torch.tensor([graph_us if graph_us is not None else -1.0], dtype=torch.float64, device=dev)
+    dist.all_reduce(gt, op=dist.ReduceOp.MAX)
+    graph_us = float(gt.item()) if float(gt.item()) > 0 else None
     t = torch.tensor(acc / iters, dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     same = ids.to(torch.int64).clone()
@@ -353,7 +377,8 @@ def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
     us = [float(v) for v in t]
     return {"rows": 128, "vocab": VOCAB, "shards": world, "local_topk_us": round(us[0], 1), "all_gather_us": round(us[1], 1),
             "merge_draw_us": round(us[2], 1), "rows_per_s": round(128 / (sum(us) * 1e-6)),
-            "all_gather_bytes_sent_per_rank": int(128 * slots * 8), "ranks_agree": bool(int(agree.item()))}
+            "all_gather_bytes_sent_per_rank": int(128 * slots * 8), "ranks_agree": bool(int(agree.item())),
+            "step_us_in_one_graph": None if graph_us is None else round(graph_us, 1)}
 
 
 def wl_logits_np(pinned):
