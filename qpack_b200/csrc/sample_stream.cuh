@@ -230,7 +230,8 @@ static __device__ int pen_build(int *tab, int slots, int *unique_ctr, const int 
   int mine = pen_insert(tab, slots, first_id, vocab_total, status, bloom);
   for (long long i = from + kThreads + threadIdx.x; i < hn; i += kThreads)
     mine += pen_insert(tab, slots, hist[i], vocab_total, status, bloom);
-  if (mine) atomicAdd(unique_ctr, mine);
+  mine = (int)__reduce_add_sync(0xffffffffu, (unsigned)mine);  // one add per warp: same-address atomics serialise
+  if ((threadIdx.x & 31) == 0 && mine) atomicAdd(unique_ctr, mine);
   __syncthreads();
   return *unique_ctr;
 }
