@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
     }
     // ---- top-p (sampler.cpp:51): first position whose running sum of e / sum reaches top_p ----
     unsigned long long keep_b = in_count;
-    MassPos cut = {false, 0u, 0ULL, 0ULL};
+    MassPos cut = {false, 0xffffffffu, 0u, 0ULL, 0ULL};
     if (p.top_p < 1.f) {
       // Masses are the numerators themselves in 2^-44 fixed point (exact for numerators >= 2^-20, the others lose
       // less than 2^-44 each: 1e-8 of the top numerator over a whole row), compared with top_p * sum: no division
@@ -174,12 +174,13 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
         }
         __syncthreads();
       } else if (keep_b < keep_a && cut.found) {
-        long long rank = ordered_rank_of_equal(c, cut.key);
+        // (compared under cut.mask: the descent stops early when a single column is left, which then stays)
+        long long rank = cut.mask == 0xffffffffu ? ordered_rank_of_equal(c, cut.key) : 0;
         for (int i = i0; i < i1; ++i) {
           const uint32_t k = keys[i];
           if (k == kExcl) continue;
-          if (k < cut.key) keys[i] = kExcl;
-          else if (k == cut.key) { if ((unsigned long long)rank >= cut.j) keys[i] = kExcl; ++rank; }
+          if ((k & cut.mask) < cut.key) keys[i] = kExcl;
+          else if ((k & cut.mask) == cut.key) { if ((unsigned long long)rank >= cut.j) keys[i] = kExcl; ++rank; }
         }
         __syncthreads();
       } else {
@@ -210,7 +211,7 @@ __global__ void __launch_bounds__(kWThreads, 1) whole_rows_kernel(const __grid_c
           return __float2ull_rz(e_of(i, k) * 0x1p44f);
         });
         if (mp.found) {
-          picked = cluster_id_of_jth(c, mp.key, mp.j, s0);
+          picked = cluster_id_of_jth(c, mp.key, mp.j, s0, mp.mask);
         } else {  // rounding left the total below u: the reference returns the last pair (sampler.cpp:62)
           uint32_t inv = 0;
           for (int i = i0; i < i1; ++i)

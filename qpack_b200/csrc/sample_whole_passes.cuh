@@ -67,10 +67,10 @@ struct NoWeight {
 };
 
 // Exclusive rank, in index order over the whole cluster, of this thread's first column with key == kk.
-__device__ __forceinline__ long long ordered_rank_of_equal(WholeCtx &c, uint32_t kk) {
+__device__ __forceinline__ long long ordered_rank_of_equal(WholeCtx &c, uint32_t kk, uint32_t kmask = 0xffffffffu) {
   const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
   int mine = 0;
-  for (int i = i0; i < i1; ++i) mine += c.keys[i] == kk;
+  for (int i = i0; i < i1; ++i) mine += c.keys[i] != kExcl && (c.keys[i] & kmask) == kk;
   int total = 0;
   const int base = block_excl_scan_int(c, mine, &total);
   unsigned long long below = 0;
@@ -135,7 +135,8 @@ __device__ void cluster_keep_top(WholeCtx &c, unsigned long long want) {
 
 struct MassPos {
   bool found;               // false: the total mass stays below the target
-  uint32_t key;             // key of the column where the running mass reaches the target
+  uint32_t mask;            // key bits that were resolved: all of them, or fewer when one column was left earlier
+  uint32_t key;             // key (under mask) of the column where the running mass reaches the target
   unsigned long long pos;   // 1-based position of that column in the value-ordered row
   unsigned long long j;     // 1-based rank of that column among the columns of the same key, in index order
 };
@@ -150,7 +151,7 @@ __device__ MassPos cluster_mass_find(WholeCtx &c, unsigned long long target, Wei
   if (target == 0ULL) target = 1ULL;
   uint32_t prefix = 0, mask = 0;
   unsigned long long w_above = 0, g_above = 0, bucket_w = 0, bucket_n = 0;
-  MassPos out = {false, 0u, 0ULL, 0ULL};
+  MassPos out = {false, 0xffffffffu, 0u, 0ULL, 0ULL};
   for (int shift = 24; shift >= 0; shift -= 8) {
     cluster_hist_pass<true>(c, prefix, mask, shift, wf);
     if (threadIdx.x == 0) S->sel[2] = 0u;
@@ -204,6 +205,14 @@ __device__ MassPos cluster_mass_find(WholeCtx &c, unsigned long long target, Wei
     if (!hit) return out;
     prefix |= d << shift;
     mask |= 0xffu << shift;
+    if (bucket_n == 1ULL && shift > 0) {  // one column left: it is the crossing, the lower digits need no pass
+      out.found = true;
+      out.mask = mask;
+      out.key = prefix;
+      out.pos = g_above + 1ULL;
+      out.j = 1ULL;
+      return out;
+    }
   }
   // all bucket_n columns of key `prefix` carry the same mass
   const unsigned long long each = bucket_n ? bucket_w / bucket_n : 0ULL;
@@ -218,8 +227,9 @@ __device__ MassPos cluster_mass_find(WholeCtx &c, unsigned long long target, Wei
 }
 
 // Global id of the j-th (1-based) column with key kk in index order; the same value in every thread of the cluster.
-__device__ int cluster_id_of_jth(WholeCtx &c, uint32_t kk, unsigned long long j, int first_global_id) {
-  const long long rank0 = ordered_rank_of_equal(c, kk);
+__device__ int cluster_id_of_jth(WholeCtx &c, uint32_t kk, unsigned long long j, int first_global_id,
+                                 uint32_t kmask = 0xffffffffu) {
+  const long long rank0 = ordered_rank_of_equal(c, kk, kmask);
   const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
   const int slot = c.xslot;
   c.xslot ^= 1;
@@ -227,7 +237,7 @@ __device__ int cluster_id_of_jth(WholeCtx &c, uint32_t kk, unsigned long long j,
   __syncthreads();
   long long rank = rank0;
   for (int i = i0; i < i1; ++i)
-    if (c.keys[i] == kk) {
+    if (c.keys[i] != kExcl && (c.keys[i] & kmask) == kk) {
       if ((unsigned long long)rank + 1ULL == j) c.S->xch[slot][3] = (unsigned long long)(first_global_id + i) + 1ULL;
       ++rank;
     }
