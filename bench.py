@@ -276,7 +276,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- vocabulary-sharded step (config 5), N > 1 only: latency-bound, reported by phase ----
     if dist is not None:
-        sh = bench_vocab_sharded(torch, dist, dev, local_rank, rank, world)
+        sh = bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, graph=args.sharded_graph)
         if rank == 0:
             extra["vocab_sharded"] = sh
 
@@ -312,7 +312,7 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
+def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30, graph=False):
     """Config 5 over the ranks of this run: 128 rows, V = 151936 split into contiguous column shards, local top-64
     per shard -> one all-gather -> merge, filter and draw.  Device time per phase (CUDA events on the current
     stream, max over ranks); every rank must end up with the same ids."""
@@ -345,6 +345,8 @@ def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
     # the same step, ten times over, captured in one CUDA graph (kernel -> all-gather -> kernel, no host in between)
     graph_us = None
     try:
+        if not graph:
+            raise RuntimeError("not requested (--sharded-graph)")
         side = torch.cuda.Stream(dev)
         side.wait_stream(stream)
         with torch.cuda.stream(side):
@@ -362,7 +364,8 @@ def bench_vocab_sharded(torch, dist, dev, local_rank, rank, world, iters=30):
             graph_us = e0.elapsed_time(e1) * 1e3 / 10
     except Exception as exc:  # capture of the collective is not available: the per-phase numbers stand alone
         graph_us = None
-        sys.stderr.write(f"vocab-sharded graph capture skipped: {exc}\n")
+        if graph:
+            sys.stderr.write(f"vocab-sharded graph capture skipped: {exc}\n")
     bs.check()
     bs.close()
     gt = torch.tensor([graph_us if graph_us is not None else -1.0], dtype=torch.float64, device=dev)
@@ -393,6 +396,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=1024)
     ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--sharded-graph", action="store_true", dest="sharded_graph",
+                    help="N > 1: also time the vocabulary-sharded step captured in one CUDA graph (NCCL inside the capture)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0, dest="cpu_seconds")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
