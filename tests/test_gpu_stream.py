@@ -339,3 +339,13 @@ def test_full_size_batch_properties():
     bs.check()
     bs.close()
     assert np.array_equal(g, np.argmax(wl.logits, axis=1).astype(np.int32))
+
+
+def test_more_rows_than_resident_ctas():
+    """2300 rows in one call: more CTAs than the GPU holds at once (three waves of the 128-thread build), so rows
+    start while others finish; every row equals the checker."""
+    wl = synth.serving_batch(rows=2300, vocab=32768)
+    exp = Oracle.sample_rows(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    got = run_device(wl.params, wl.logits, wl.history, wl.hist_len, max_out=64)
+    rep = compare_rows(*got, exp)
+    assert rep["id_mismatch"] == 0 and rep["p_bit_diff"] == 0, rep
