@@ -158,8 +158,9 @@ QPB_API int qpb_sampler_set_stream_config(qpb_sampler *s, int threads, int log2_
 QPB_API int qpb_sampler_set_debug(qpb_sampler *s, int flags);
 
 /* Row pieces: the tiles of all rows of a call laid end to end and dealt out in equal runs to as many CTAs as fit on
- * the GPU, rows that straddle two CTAs merged through device scratch (allocated on first use).  mode 0 (default):
- * only when whole rows would leave the last wave of CTAs less than a quarter full; 1: always; -1: never. */
+ * the GPU, rows that straddle two CTAs merged through device scratch (allocated on first use).  mode 1: on;
+ * 0 (default) and -1: off (whole rows measured faster at every batch size tried; kept as a tested alternative
+ * schedule). */
 QPB_API int qpb_sampler_set_pieces(qpb_sampler *s, int mode);
 
 /* Latency breakdown aid.  enable != 0 turns on per-row phase stamps (SM clock of the row's leader CTA:

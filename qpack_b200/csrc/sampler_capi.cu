@@ -150,9 +150,28 @@ size_t stream_smem(const StreamPlan &pl, int pen_slots, int cluster = 1) {
   return off + (size_t)(cluster - 1) * (kSmallMaxM * sizeof(unsigned long long) + 2 * sizeof(int));
 }
 constexpr size_t kSmemLimit = 227 * 1024;
+// Estimated time of `rows` whole rows in waves of `slots` resident CTAs, from a linear fit of measured waves at
+// V = 151936 (microseconds: a wave costs `fixed` plus `per_row` for each of its rows); only the comparison of the
+// two builds matters.
+double waves_estimate(long long rows, long long slots, double fixed, double per_row) {
+  const long long full = rows / slots, rem = rows % slots;
+  return (double)full * (fixed + per_row * (double)slots) + (rem ? fixed + per_row * (double)rem : 0.0);
+}
 StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots, int cluster = 1) {
   StreamPlan pl;
-  pl.nt = s->force_threads ? s->force_threads : (ctas > 4LL * s->sm_count ? 128 : 256);
+  pl.nt = 256;
+  if (s->force_threads) {
+    pl.nt = s->force_threads;
+  } else if (ctas > 4LL * s->sm_count) {
+    // More CTAs than the 256-thread build keeps resident: the 128-thread build holds more rows per wave (7 per SM
+    // with a small penalty table), but a nearly empty last wave costs it more, so both are estimated.
+    StreamPlan p128 = {128, 1};
+    long long per_sm = (long long)(kSmemLimit / (stream_smem(p128, pen_slots) + 1024));
+    per_sm = per_sm > 8 ? 8 : (per_sm < 1 ? 1 : per_sm);
+    const double t128 = waves_estimate(ctas, per_sm * s->sm_count, 42.0, 0.068);
+    const double t256 = waves_estimate(ctas, 4LL * s->sm_count, 20.0, 0.0815);
+    pl.nt = t128 <= t256 ? 128 : 256;
+  }
   if (s->force_log2_stages) pl.lg = s->force_log2_stages;
   else pl.lg = (pl.nt == 256 && cluster > 1 && ctas <= 2LL * s->sm_count) ? 2 : 1;
   // (four stages let a cluster CTA fetch the head of its short slice once and use it as its threshold sample;
@@ -183,9 +202,8 @@ int plan_pieces(qpb_sampler *s, StreamArgs &a, int n_rows, int *ctas, int *nt_ou
   if (s->pieces < 0 || s->cluster || s->d_phase_clk || n_rows < 2) return QPB_OK;
   const int nt = plan_stream(s, n_rows, a.pen_slots).nt;
   const int slots = (1024 / nt) * s->sm_count;
-  // Pieces cost a threshold bootstrap, a cut and a trip through scratch each, so whole rows win unless their last
-  // wave would leave most of the GPU idle.
-  if (s->pieces == 0 && (n_rows <= slots || (n_rows % slots) * 4 > slots || n_rows % slots == 0)) return QPB_OK;
+  // Pieces cost a threshold bootstrap, a cut and a trip through scratch each.
+  if (s->pieces == 0) return QPB_OK;  // on request only: measured slower than whole rows at every batch size tried
   const int tile = nt * 16;
   const long long tpr = (a.vocab + tile - 1) / tile;
   const long long total = (long long)n_rows * tpr;
