@@ -99,9 +99,10 @@ long long row_budget(const qpb_sampler_params &p, int vocab_total) {
   return K + window;
 }
 
-int pen_slots_for(long long window) {
+// slots of the penalty hash table: a power of two, at least `per_id` slots per window id
+int pen_slots_for(long long window, int per_id = 2) {
   int slots = 64;
-  while (slots < 2 * window && slots < (1 << 20)) slots <<= 1;
+  while (slots < per_id * window && slots < (1 << 20)) slots <<= 1;
   return slots;
 }
 
@@ -270,6 +271,9 @@ int launch_stream_nt(qpb_sampler *s, const StreamArgs &args, int rows, int clust
 template <int MODE>
 int launch_stream(qpb_sampler *s, const StreamArgs &args_in, int rows, int cluster, cudaStream_t st, int nt) {
   StreamArgs args = args_in;
+  // A small launch has shared memory to spare: a sparser penalty table (8 slots per window id instead of 2) keeps the
+  // probe sequences of the 256 simultaneous inserts short, which is on the critical path of a lone row.
+  if ((long long)rows * cluster <= 2LL * s->sm_count && s->max_window <= 1024) args.pen_slots = pen_slots_for(s->max_window, 8);
   StreamPlan pl = plan_stream(s, (long long)rows * cluster, args.pen_slots, cluster);
   if (nt) {  // the caller counted tiles for this block size
     pl.nt = nt;
