@@ -635,8 +635,8 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
       s1 = min(a.vocab, s0 + per);
       if (csize > 1 && per >= 4 * kTile) {
         // The leader also builds the penalty set and fetches the random words, which makes it the last to reach
-        // the cluster's barrier: its slice is two tiles shorter (but three tiles at least), the others share the rest.
-        const int lead = max(3 * kTile, per - 2 * kTile);
+        // the cluster's barrier: its slice is one tile shorter (but three tiles at least), the others share the rest.
+        const int lead = max(3 * kTile, per - kTile);
         int rest = (a.vocab - lead + csize - 2) / (csize - 1);
         rest = (rest + 3) & ~3;
         s0 = crank == 0 ? 0 : min(a.vocab, lead + (crank - 1) * rest);

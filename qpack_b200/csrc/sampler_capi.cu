@@ -174,7 +174,7 @@ StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots, int 
     pl.nt = t128 <= t256 ? 128 : 256;
   }
   if (s->force_log2_stages) pl.lg = s->force_log2_stages;
-  else pl.lg = (pl.nt == 256 && cluster > 1 && ctas <= 2LL * s->sm_count) ? 2 : 1;
+  else pl.lg = (pl.nt == 256 && cluster > 1 && 10LL * ctas <= 18LL * s->sm_count) ? 2 : 1;  // two per SM, with slack
   // (four stages let a cluster CTA fetch the head of its short slice once and use it as its threshold sample;
   // otherwise deeper rings measured no faster: one CTA is bound by its own scan, many CTAs by HBM)
   while (pl.lg > 1 && stream_smem(pl, pen_slots, cluster) > kSmemLimit) pl.lg--;
@@ -186,9 +186,10 @@ int merge_cap(int nt) { return nt == 128 ? Stream<128>::kMergeCap : Stream<256>:
 int pick_cluster(const qpb_sampler *s, int rows) {
   // A single CTA takes a few tens of microseconds over a row, so while SMs are to spare a row is split over a
   // cluster, as wide as the shared memory of its CTAs (the leader's inbox grows with the cluster) lets the launch
-  // stay resident at once: 8 CTAs up to two CTAs per SM, 4 up to three, 2 up to four (measured best).
+  // stay resident at once: 8 CTAs up to 1.75 CTAs per SM, 4 up to 2.7 (cluster placement needs slack), 2 up to four
+  // (measured best).
   int c = s->cluster;
-  if (!c) c = 8LL * rows <= 2LL * s->sm_count ? 8 : (4LL * rows <= 3LL * s->sm_count ? 4 : (2LL * rows <= 4LL * s->sm_count ? 2 : 1));
+  if (!c) c = 32LL * rows <= 7LL * s->sm_count ? 8 : (40LL * rows <= 27LL * s->sm_count ? 4 : (2LL * rows <= 4LL * s->sm_count ? 2 : 1));
   const int nt = plan_stream(s, (long long)rows * c, 64).nt;
   return c < max_cluster(nt) ? c : max_cluster(nt);
 }
@@ -273,8 +274,18 @@ int launch_stream(qpb_sampler *s, const StreamArgs &args_in, int rows, int clust
   StreamArgs args = args_in;
   // A small launch has shared memory to spare: a sparser penalty table (8 slots per window id instead of 2) keeps the
   // probe sequences of the 256 simultaneous inserts short, which is on the critical path of a lone row.
-  if ((long long)rows * cluster <= 2LL * s->sm_count && s->max_window <= 1024) args.pen_slots = pen_slots_for(s->max_window, 8);
+  // (only where the launch still fits on the GPU at once with it)
+  const int dense_slots = args.pen_slots;
+  if (10LL * rows * cluster <= 18LL * s->sm_count && s->max_window <= 1024) args.pen_slots = pen_slots_for(s->max_window, 8);
   StreamPlan pl = plan_stream(s, (long long)rows * cluster, args.pen_slots, cluster);
+  if (args.pen_slots != dense_slots) {
+    const long long per_sm = (long long)(kSmemLimit / (stream_smem(pl, args.pen_slots, cluster) + 1024));
+    // (clusters need their CTAs on free SMs of one GPC, so a launch that only just fits by the count does not)
+    if (per_sm < 2 && 2LL * rows * cluster > s->sm_count) {
+      args.pen_slots = dense_slots;
+      pl = plan_stream(s, (long long)rows * cluster, args.pen_slots, cluster);
+    }
+  }
   if (nt) {  // the caller counted tiles for this block size
     pl.nt = nt;
     if (nt == 128) pl.lg = 1;
