@@ -228,6 +228,7 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
     // selects whenever another chunk might not fit, so the list can never overflow whatever the data.
     for (int attempt = 0; attempt < 3; ++attempt) {
       bool careful = false;
+      int level_acc = 0;  // list fill level over a run of tiles without a barrier
       for (int t = 0; t < n_tiles;) {
         const int g = g0 + t;
         const int st = g & (nst - 1);
@@ -280,8 +281,26 @@ __device__ void Stream<NT>::run(const StreamArgs &a) {
             }
             if (nacc) level = pos > kCandCap ? 3 : (pos > kCandHighFast ? 1 : 0);
           }
+          // When the ring holds the whole piece no stage is ever refilled, so nothing has to be settled between two
+          // full tiles: the barrier waits for the end of the run (a short slice of a cluster CTA is one run).
+          if (n_tiles <= nst && t + 1 < n_tiles && tile_len(t + 1) == kTile) {
+            level_acc |= level;
+            ++t;
+            continue;
+          }
           // stage consumed by every thread; candidate count settled; the highest slot taken tells how full the list is
-          const int fill = __syncthreads_or(level);
+          const int fill = __syncthreads_or(level | level_acc);
+          level_acc = 0;
+          if ((fill & 2) && n_tiles <= nst) {
+            // more survivors than the list holds, somewhere in the run: start the piece over, chunk by chunk (its
+            // tiles are all still in the ring)
+            __syncthreads();
+            if (tid == 0) S.cand_count = 0;
+            careful = true;
+            t = 0;
+            __syncthreads();
+            continue;
+          }
           if (fill & 2) {
             // more survivors than the list holds: forget this tile's, scan it again chunk by chunk
             __syncthreads();

@@ -174,6 +174,8 @@ StreamPlan plan_stream(const qpb_sampler *s, long long ctas, int pen_slots, int 
     pl.nt = t128 <= t256 ? 128 : 256;
   }
   if (s->force_log2_stages) pl.lg = s->force_log2_stages;
+  else if (pl.nt == 256 && cluster > 1 && 2LL * ctas <= s->sm_count) pl.lg = 3;  // at most half the SMs: a ring that holds
+                                                                                          // a cluster CTA's whole slice
   else pl.lg = (pl.nt == 256 && cluster > 1 && 10LL * ctas <= 18LL * s->sm_count) ? 2 : 1;  // two per SM, with slack
   // (four stages let a cluster CTA fetch the head of its short slice once and use it as its threshold sample;
   // otherwise deeper rings measured no faster: one CTA is bound by its own scan, many CTAs by HBM)
