@@ -148,7 +148,8 @@ QPB_API int qpb_sampler_set_cluster(qpb_sampler *s, int cluster);
 
 /* Streaming kernel configuration (tuning and tests; no counterpart in the reference): threads per CTA (128 or 256)
  * and log2 of the shared-memory ring depth (1 to 3).  0 = chosen per launch from the number of rows (default):
- * 256 threads for up to four CTAs per SM, 128 threads and eight CTAs per SM beyond, a ring of two stages.
+ * 256 threads for up to four CTAs per SM, beyond that whichever build a wave-by-wave estimate favours (128 threads
+ * hold seven to eight CTAs per SM); a ring of two stages, four or eight for small cluster launches.
  * With 128 threads a cluster holds at most 4 CTAs. */
 QPB_API int qpb_sampler_set_stream_config(qpb_sampler *s, int threads, int log2_stages);
 
