@@ -33,8 +33,8 @@ struct WholeArgs {
 
 struct __align__(16) WholeSmem {
   uint32_t hist[256];                // this CTA's count histogram (read by the whole cluster)
-  uint32_t whist[4][256];            // this CTA's mass histogram in four 16-bit limbs (32-bit adds only; a CTA makes
-                                     // fewer than 2^15 additions of < 2^16 each per limb and bin)
+  uint32_t whist[3][256];            // this CTA's mass histogram in three 17-bit limbs (32-bit adds only: a run's mass
+                                     // stays below 2^51, a CTA makes fewer than 2^15 additions of < 2^17 per limb and bin)
   uint32_t thist[256];               // cluster totals, computed redundantly by every CTA
   unsigned long long twhist[256];
   unsigned long long xch[2][4];      // scalar exchange slots (read by the whole cluster), double-buffered

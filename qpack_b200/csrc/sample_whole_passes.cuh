@@ -13,7 +13,7 @@ __device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, 
   WholeSmem *S = c.S;
   if (threadIdx.x < 256) {
     S->hist[threadIdx.x] = 0;
-    if (WEIGHTED) { S->whist[0][threadIdx.x] = 0u; S->whist[1][threadIdx.x] = 0u; S->whist[2][threadIdx.x] = 0u; S->whist[3][threadIdx.x] = 0u; }
+    if (WEIGHTED) { S->whist[0][threadIdx.x] = 0u; S->whist[1][threadIdx.x] = 0u; S->whist[2][threadIdx.x] = 0u; }
   }
   __syncthreads();
   const int i0 = threadIdx.x * c.per_t, i1 = min(c.n, i0 + c.per_t);
@@ -23,11 +23,10 @@ __device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, 
   unsigned long long run_w = 0;
   auto flush = [&](uint32_t d, uint32_t n, unsigned long long w) {
     atomicAdd(&S->hist[d], n);
-    if (WEIGHTED) {  // 64-bit shared-memory adds are slow under contention: four 32-bit adds of 16-bit limbs instead
-      atomicAdd(&S->whist[0][d], (uint32_t)(w & 0xffffULL));
-      atomicAdd(&S->whist[1][d], (uint32_t)((w >> 16) & 0xffffULL));
-      atomicAdd(&S->whist[2][d], (uint32_t)((w >> 32) & 0xffffULL));
-      atomicAdd(&S->whist[3][d], (uint32_t)(w >> 48));
+    if (WEIGHTED) {  // 64-bit shared-memory adds are slow under contention: three 32-bit adds of 17-bit limbs instead
+      atomicAdd(&S->whist[0][d], (uint32_t)(w & 0x1ffffULL));
+      atomicAdd(&S->whist[1][d], (uint32_t)((w >> 17) & 0x1ffffULL));
+      atomicAdd(&S->whist[2][d], (uint32_t)(w >> 34));
     }
   };
   for (int i = i0; i < i1; ++i) {
@@ -53,8 +52,8 @@ __device__ __forceinline__ void cluster_hist_pass(WholeCtx &c, uint32_t prefix, 
       const WholeSmem *R = cooperative_groups::this_cluster().map_shared_rank(S, r);
       t += R->hist[threadIdx.x];
       if (WEIGHTED)
-        tw += (unsigned long long)R->whist[0][threadIdx.x] + ((unsigned long long)R->whist[1][threadIdx.x] << 16) +
-              ((unsigned long long)R->whist[2][threadIdx.x] << 32) + ((unsigned long long)R->whist[3][threadIdx.x] << 48);
+        tw += (unsigned long long)R->whist[0][threadIdx.x] + ((unsigned long long)R->whist[1][threadIdx.x] << 17) +
+              ((unsigned long long)R->whist[2][threadIdx.x] << 34);
     }
     S->thist[threadIdx.x] = t;
     if (WEIGHTED) S->twhist[threadIdx.x] = tw;
